@@ -1,0 +1,56 @@
+// ggq_gemv: argument checking and kernel selection for the small-batch fused multiply.
+#include "gemv.cuh"
+
+using namespace ggq;
+
+namespace {
+constexpr int kGemvMaxBatch = 16;
+}
+
+extern "C" int32_t ggq_gemv_max_batch(void) { return kGemvMaxBatch; }
+
+extern "C" int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K) {
+  const TypeInfo* ti = type_info(qtype);
+  if (!ti || !ti->fused || N <= 0 || K <= 0 || K % ti->block_elems) return 0;
+  return kGemvMaxBatch;
+}
+
+extern "C" size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32_t M) {
+  (void)qtype; (void)N; (void)K; (void)M;
+  return 0;
+}
+
+extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
+                            int32_t M, void* y, int32_t y_dtype, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  (void)workspace; (void)workspace_bytes;
+  const TypeInfo* ti = type_info(qtype);
+  if (!ti) return fail(GGQ_BAD_QTYPE, "ggq_gemv: qtype %d is not decodable", qtype);
+  if (!ti->fused) return fail(GGQ_UNSUPPORTED, "ggq_gemv: no fused kernel for qtype %d", qtype);
+  if (N <= 0 || K <= 0 || K % ti->block_elems)
+    return fail(GGQ_BAD_SHAPE, "ggq_gemv: N=%lld K=%lld (K must be a positive multiple of %d)",
+                (long long)N, (long long)K, ti->block_elems);
+  if (M < 1 || M > kGemvMaxBatch)
+    return fail(GGQ_BAD_SHAPE, "ggq_gemv: M=%d outside 1..%d", M, kGemvMaxBatch);
+  if (y_dtype != GGQ_F32 && y_dtype != GGQ_BF16 && y_dtype != GGQ_F16)
+    return fail(GGQ_BAD_DTYPE, "ggq_gemv: y_dtype %d", y_dtype);
+  if (!w || !x_bf16 || !y) return fail(GGQ_MISALIGNED, "ggq_gemv: null pointer");
+  if ((uintptr_t)x_bf16 % 16) return fail(GGQ_MISALIGNED, "ggq_gemv: x must be 16-byte aligned");
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const uint8_t* tab = device_tables(dev);
+  if (ti->needs_tables && !tab)
+    return fail(GGQ_NO_TABLES, "ggq_gemv: call ggq_set_tables(%d, ...) before using qtype %d", dev, qtype);
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t err = gemv_generic(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, st);
+  if (err != cudaSuccess) return fail(GGQ_LAUNCH_FAILED, "ggq_gemv: %s", cudaGetErrorString(err));
+  return GGQ_OK;
+}
+
+extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
+                            int32_t M, void* y, int32_t y_dtype, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  (void)w; (void)N; (void)K; (void)x_bf16; (void)M; (void)y; (void)y_dtype;
+  (void)workspace; (void)workspace_bytes; (void)stream;
+  return fail(GGQ_UNSUPPORTED, "ggq_gemm: no tensor-core kernel for qtype %d yet", qtype);
+}

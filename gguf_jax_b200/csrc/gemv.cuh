@@ -1,0 +1,19 @@
+// Internal interface between the multiply kernels and the ggq_gemv / ggq_gemm entry points.
+#pragma once
+
+#include "ggq_common.cuh"
+
+namespace ggq {
+
+// Single rounding of a float32 result to the caller's output dtype.
+__device__ __forceinline__ void store_out(void* y, int y_dtype, int64_t idx, float v) {
+  if (y_dtype == GGQ_F32) reinterpret_cast<float*>(y)[idx] = v;
+  else if (y_dtype == GGQ_BF16) reinterpret_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
+  else reinterpret_cast<__half*>(y)[idx] = __float2half_rn(v);
+}
+
+// Coverage kernel: any block qtype, any M <= 16 (gemv_generic.cu).
+cudaError_t gemv_generic(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K, const void* x, int M,
+                         void* y, int y_dtype, const uint8_t* tab, cudaStream_t st);
+
+}  // namespace ggq

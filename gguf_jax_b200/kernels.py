@@ -1,0 +1,123 @@
+"""Fused multiply kernels: ``x @ w.T`` with ``w`` kept quantized in HBM.
+
+Host-side wrappers over ``ggq_gemv`` / ``ggq_gemm`` (include/ggq.h).  They stand where the
+reference's ``matmul_q4_k``, ``matmul_q5_k``, ``matmul_q6_k``, ``matmul_iq4_xs``,
+``matmul_lowbit`` and ``gemm_q4_k`` stand (src/gguf_jax/cute/*.py) and keep their
+calling convention: ``x`` is bfloat16 ``(..., K)``, ``w`` a 2-D ``QuantizedArray (N, K)``,
+the result is bfloat16 ``(..., N)``.
+
+Numerical contract: weights enter at full float32 precision (integer codes times float32
+scales), accumulation is float32 and the only narrow rounding is the output, so the
+result tracks the float32 ``dequant_matmul`` within relative L2 2e-3 and a one-hot ``x``
+reproduces ``bf16(float32 weight)`` exactly.
+"""
+from __future__ import annotations
+
+import torch
+from gguf.constants import GGMLQuantizationType as QT
+
+from . import _backend, _lib
+from .array import QuantizedArray
+
+__all__ = [
+    "LOWBIT_TYPES", "fused_matmul", "gemv_max_batch", "matmul_q4_k", "matmul_q5_k", "matmul_q6_k",
+    "matmul_iq4_xs", "matmul_lowbit", "gemm_q4_k", "dequantize_q4_k", "register",
+]
+
+# The eight types the reference's low-bit template covers (src/gguf_jax/cute/lowbit.py).
+LOWBIT_TYPES = (QT.Q2_K, QT.IQ1_S, QT.IQ1_M, QT.IQ2_XXS, QT.IQ2_XS, QT.IQ2_S, QT.IQ3_XXS, QT.IQ3_S)
+
+
+def gemv_max_batch() -> int:
+    """Largest flattened batch served by the small-batch kernel (``ggq_gemv``)."""
+    return int(_lib.lib().ggq_gemv_max_batch())
+
+
+def _check(x: torch.Tensor, w: QuantizedArray, qtypes=None) -> tuple[int, int]:
+    if not isinstance(w, QuantizedArray):
+        raise TypeError(f"expected a QuantizedArray weight, got {type(w).__name__}")
+    if qtypes is not None and w.qtype not in qtypes:
+        raise ValueError(f"this kernel handles {[t.name for t in qtypes]}, got {w.qtype.name}")
+    if len(w.shape) != 2:
+        raise ValueError(f"w must be 2D, got shape {w.shape}")
+    n_rows, k_dim = w.shape
+    if x.shape[-1] != k_dim:
+        raise ValueError(f"contraction mismatch: x has {x.shape[-1]}, w has {k_dim}")
+    if x.dtype != torch.bfloat16:
+        raise ValueError(f"x must be bfloat16, got {x.dtype}")
+    return n_rows, k_dim
+
+
+def fused_matmul(x: torch.Tensor, w: QuantizedArray, *, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``x @ w.T`` through the fused kernels, whatever the batch: the small-batch kernel up
+    to ``gemv_max_batch()``, the tensor-core kernel above it."""
+    n_rows, k_dim = _check(x, w)
+    dev = _backend.require_cuda(w.data, f"fused matmul ({w.qtype.name})")
+    if x.device != w.data.device:
+        raise ValueError(f"x is on {x.device}, w on {w.data.device}")
+    _lib.ensure_tables(dev)
+    L = _lib.lib()
+    out_dtype = _backend.canon_dtype(out_dtype)
+    xm = x.reshape(-1, k_dim).contiguous()
+    m = xm.shape[0]
+    data = w.data.contiguous()
+    y = torch.empty((m, n_rows), dtype=out_dtype, device=x.device)
+    if m == 0:
+        return y.reshape(*x.shape[:-1], n_rows)
+    fn = L.ggq_gemv if m <= L.ggq_gemv_max_batch() else L.ggq_gemm
+    with torch.cuda.device(dev):
+        need = L.ggq_workspace_bytes(int(w.qtype), n_rows, k_dim, m)
+        ws = _backend.workspace(dev, need)
+        _lib.check(fn(int(w.qtype), data.data_ptr(), n_rows, k_dim, xm.data_ptr(), m, y.data_ptr(),
+                      _backend.dtype_code(out_dtype), ws.data_ptr() if ws is not None else None,
+                      ws.numel() if ws is not None else 0, _backend.stream_ptr(dev)))
+    return y.reshape(*x.shape[:-1], n_rows)
+
+
+def matmul_q4_k(x, w, *, force_fused: bool = False):
+    """Q4_K fused multiply (stands for src/gguf_jax/cute/q4_k.py:282-329)."""
+    _check(x, w, (QT.Q4_K,))
+    return fused_matmul(x, w)
+
+
+def matmul_q5_k(x, w):
+    """Q5_K fused multiply (src/gguf_jax/cute/q5_k.py:150-179)."""
+    _check(x, w, (QT.Q5_K,))
+    return fused_matmul(x, w)
+
+
+def matmul_q6_k(x, w):
+    """Q6_K fused multiply (src/gguf_jax/cute/q6_k.py:115-144)."""
+    _check(x, w, (QT.Q6_K,))
+    return fused_matmul(x, w)
+
+
+def matmul_iq4_xs(x, w):
+    """IQ4_XS fused multiply (src/gguf_jax/cute/iq4_xs.py:146-175)."""
+    _check(x, w, (QT.IQ4_XS,))
+    return fused_matmul(x, w)
+
+
+def matmul_lowbit(x, w):
+    """Fused multiply for the eight low-bit types (src/gguf_jax/cute/lowbit.py:675-712)."""
+    _check(x, w, LOWBIT_TYPES)
+    return fused_matmul(x, w)
+
+
+def gemm_q4_k(x, w):
+    """Q4_K tensor-core multiply for larger batches (src/gguf_jax/cute/q4_k_gemm.py:369-391)."""
+    _check(x, w, (QT.Q4_K,))
+    return fused_matmul(x, w)
+
+
+def dequantize_q4_k(data, dtype=torch.float32):
+    """Q4_K bytes ``(..., row_bytes)`` -> ``dtype`` ``(..., n)`` (src/gguf_jax/cute/q4_k.py:93-101)."""
+    from . import quants
+
+    return quants.dequantize(data, QT.Q4_K, dtype)
+
+
+def register() -> None:
+    """Kept for drop-in compatibility with ``gguf_jax.cute.register``: the CUDA decode
+    kernels are already the registered decoders, so there is nothing to replace."""
+    return None

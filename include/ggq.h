@@ -1,0 +1,118 @@
+/*
+ * ggq.h -- C ABI of the B200 (sm_100a) dequantize-and-multiply library, libggq_b200.so.
+ *
+ * Every entry point is plain C: pointers, sizes and integer codes only.  All device
+ * pointers are caller-owned; the library never allocates or frees the caller's buffers,
+ * never synchronises a stream and never reads results back, so every launcher can be
+ * enqueued from a framework's custom-call handler (XLA FFI, torch, raw CUDA).
+ *
+ * qtype codes are the GGMLQuantizationType values of gguf-py / llama.cpp
+ * (gguf/constants.py), e.g. Q4_K = 12, Q6_K = 14, IQ4_XS = 23.
+ *
+ * Every function that returns int32_t returns a ggq_status; 0 is success.  On failure a
+ * thread-local message is available from ggq_last_error().  Nothing throws or exits.
+ *
+ * Each declaration names the interface of the reference project (nshepperd/gguf-jax) it
+ * stands in for, as path:line inside that project.
+ */
+#ifndef GGQ_H_
+#define GGQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ggq_status {
+  GGQ_OK = 0,
+  GGQ_BAD_QTYPE = 1,      /* qtype is not one of the 26 decodable types            */
+  GGQ_BAD_SHAPE = 2,      /* K not a multiple of the block, N/M out of range, ...  */
+  GGQ_MISALIGNED = 3,     /* a base pointer is not aligned as the kernel needs     */
+  GGQ_UNSUPPORTED = 4,    /* no fused kernel for this qtype / batch                */
+  GGQ_LAUNCH_FAILED = 5,  /* the CUDA runtime refused the launch                   */
+  GGQ_TIMEOUT = 6,        /* a bounded device-side wait ran out (see ggq_read_status) */
+  GGQ_NO_TABLES = 7,      /* a codebook qtype was used before ggq_set_tables       */
+  GGQ_BAD_WORKSPACE = 8,  /* workspace missing or too small                        */
+  GGQ_BAD_DTYPE = 9       /* output dtype code not one of ggq_dtype                */
+} ggq_status;
+
+typedef enum ggq_dtype { GGQ_F32 = 0, GGQ_BF16 = 1, GGQ_F16 = 2 } ggq_dtype;
+
+/* Library ABI version (major * 100 + minor). No reference counterpart. */
+int32_t ggq_version(void);
+
+/* Message for the last non-zero status returned on this host thread. */
+const char* ggq_last_error(void);
+
+/* Block geometry of a qtype: elements per block and bytes per block.
+ * Replaces the GGML_QUANT_SIZES lookups at src/gguf_jax/quants.py:720 and
+ * src/gguf_jax/array.py:101. */
+int32_t ggq_type_info(int32_t qtype, int32_t* block_elems, int32_t* block_bytes);
+
+/* Byte size and layout of the codebook blob ggq_set_tables expects.  The blob is the
+ * concatenation, in this order, of: IQ2_XXS grid u8[256*8], IQ2_XS grid u8[512*8],
+ * IQ2_S grid u8[1024*8], IQ3_XXS grid u8[256*4], IQ3_S grid u8[512*4],
+ * IQ1_S/IQ1_M grid i8[2048*8], IQ4_NL/IQ4_XS values i8[16], MXFP4/NVFP4 values i8[16].
+ * The host side fills it from gguf.quants at import time, exactly where the reference
+ * reads the same tables (src/gguf_jax/quants.py:476-483, cute/lowbit.py:401-420). */
+size_t ggq_tables_bytes(void);
+
+/* Upload the codebook blob (host memory) to `device` once.  The library keeps this one
+ * immutable allocation per device until the process exits.  Idempotent. */
+int32_t ggq_set_tables(int32_t device, const void* host_blob, size_t bytes);
+
+/* Decode n_blocks blocks of `qtype` (device bytes, n_blocks * block_bytes) into
+ * n_blocks * block_elems values of out_dtype on `stream`.  The float32 result is
+ * bit-identical to gguf.quants.dequantize; bf16/f16 are that result rounded once.
+ * Replaces dequantize_blocks / the 26 registered decoders
+ * (src/gguf_jax/quants.py:125-730) and the CuTe Q4_K kernel launch
+ * (src/gguf_jax/cute/q4_k.py:78-101). */
+int32_t ggq_dequant(int32_t qtype, const void* blocks, int64_t n_blocks, void* out,
+                    int32_t out_dtype, void* stream);
+
+/* 1 if a fused multiply kernel exists for qtype, else 0.
+ * Replaces the key set of _fused() (src/gguf_jax/_matmul.py:52-75). */
+int32_t ggq_has_fused(int32_t qtype);
+
+/* Largest flattened batch M that the fused route accepts for an (N, K) weight of
+ * qtype; 0 when there is none.  Replaces the per-kernel caps
+ * (src/gguf_jax/_matmul.py:60-75, cute/q4_k.py:117-118, cute/lowbit.py:97). */
+int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K);
+
+/* Largest M served by the small-batch (GEMV) kernel; above it ggq_gemm is used. */
+int32_t ggq_gemv_max_batch(void);
+
+/* Scratch the fused kernels need for an (N, K) weight at batch M.  The caller
+ * allocates at least this many bytes, 256-byte aligned, ZERO-FILLED ONCE; the kernels
+ * leave it zeroed again, so one buffer serves any number of calls that do not overlap
+ * on the GPU. */
+size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32_t M);
+
+/* y[M, N] = x[M, K] @ W[N, K]^T with W quantized (row-major blocks, N rows of
+ * K / block_elems * block_bytes bytes), x bf16, y of y_dtype, 1 <= M <= ggq_gemv_max_batch().
+ * Weights are applied at full float32 precision (exact integer codes times float32
+ * scales), accumulation is float32, the only rounding to a narrow type is the output.
+ * Replaces matmul_q4_k / matmul_q5_k / matmul_q6_k / matmul_iq4_xs / matmul_lowbit
+ * (src/gguf_jax/cute/q4_k.py:282-329, q5_k.py:150-179, q6_k.py:115-144,
+ * iq4_xs.py:146-175, lowbit.py:675-712). */
+int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
+                 int32_t M, void* y, int32_t y_dtype, void* workspace,
+                 size_t workspace_bytes, void* stream);
+
+/* Same product for larger M on the tcgen05 tensor-core path.
+ * Replaces gemm_q4_k (src/gguf_jax/cute/q4_k_gemm.py:369-391). */
+int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
+                 int32_t M, void* y, int32_t y_dtype, void* workspace,
+                 size_t workspace_bytes, void* stream);
+
+/* Reads and clears the device-side status word of `device` (0 = no bounded wait ran
+ * out since the last read).  Synchronises the device.  No reference counterpart: the
+ * reference has no device-side waits. */
+int32_t ggq_read_status(int32_t device, int32_t* status_word);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GGQ_H_ */

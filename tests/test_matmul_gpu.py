@@ -1,0 +1,160 @@
+"""Fused multiply parity on a B200, through the C ABI.
+
+Pass criteria (stated in the tests): relative L2 error <= 2e-3 against the float32
+dequant_matmul oracle; the reference's elementwise rtol=1e-2, atol=1e-2*max|ref|
+(tests/test_cute.py there); and bitwise one-hot exactness -- x = e_k must return
+bf16(float32 oracle weight[:, k]) (tests/test_cute.py:130-148, 412-424 there)."""
+import numpy as np
+import pytest
+import torch
+from gguf.constants import GGML_QUANT_SIZES
+from gguf.constants import GGMLQuantizationType as QT
+
+import gguf_jax_b200 as gj
+from gguf_jax_b200 import _matmul as mm
+from gguf_jax_b200 import kernels, synth
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+REL_L2 = 2e-3
+FUSED = gj.fused_types()
+REFERENCE_FUSED = [QT.Q4_K, QT.Q5_K, QT.Q6_K, QT.IQ4_XS, QT.Q2_K, QT.IQ1_M, QT.IQ2_XXS, QT.IQ2_XS, QT.IQ2_S,
+                   QT.IQ3_XXS, QT.IQ3_S, QT.IQ1_S]
+GOLDEN = np.load(__file__.replace("test_matmul_gpu.py", "golden/decode_golden.npz"))
+
+
+def to_x(x_f32: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(x_f32).cuda().to(torch.bfloat16)
+
+
+def run_fused(x_f32, w_bytes, qtype, out_dtype=torch.bfloat16):
+    n = w_bytes.shape[0]
+    k = x_f32.shape[-1]
+    w = gj.QuantizedArray.from_bytes(w_bytes, qtype, shape=(n, k))
+    return kernels.fused_matmul(to_x(x_f32), w, out_dtype=out_dtype).float().cpu().numpy()
+
+
+def check_close(got, ref):
+    assert O.rel_l2(got, ref) <= REL_L2, O.rel_l2(got, ref)
+    np.testing.assert_allclose(got, ref, rtol=1e-2, atol=1e-2 * np.abs(ref).max())
+
+
+@pytest.mark.parametrize("qtype", FUSED, ids=lambda t: t.name)
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 12, 16])
+def test_fused_matches_oracle(qtype, m):
+    bs = GGML_QUANT_SIZES[qtype][0]
+    n, k = 200, 11 * 256           # N not a tile multiple, rows only 2-byte aligned for most types
+    w = synth.make_weight_bytes(n, k, qtype, seed=m)
+    x = synth.make_x(m, k, seed=m)
+    ref = O.c_matmul(O.bf16_bits(x), w, qtype)
+    check_close(run_fused(x, w, qtype), ref)
+    got32 = run_fused(x, w, qtype, torch.float32)
+    assert O.rel_l2(got32, ref) <= 2e-5   # before the output rounding the kernel is float32-exact
+
+
+@pytest.mark.parametrize("qtype", FUSED, ids=lambda t: t.name)
+def test_golden_matmul(qtype):
+    w, x, y = (GOLDEN[f"{qtype.name}.mm.{k}"] for k in ("w", "x", "y"))
+    check_close(run_fused(x, w, qtype), y)
+
+
+@pytest.mark.parametrize("qtype", FUSED, ids=lambda t: t.name)
+def test_one_hot_exactness(qtype):
+    bs = GGML_QUANT_SIZES[qtype][0]
+    n, k = 24, 11 * 256
+    w = synth.make_weight_bytes(n, k, qtype, seed=42)
+    W = O.ref_dequantize(w, qtype)
+    want = torch.from_numpy(W).to(torch.bfloat16).float().numpy()
+    cols = [0, 1, 3, 4, 15, 16, 31, 32, 33, 63, 64, 127, 128, 255, 256, 257, 1000, k - 1]
+    for lo in range(0, len(cols), 16):
+        sel = cols[lo:lo + 16]
+        x = np.zeros((len(sel), k), dtype=np.float32)
+        x[np.arange(len(sel)), sel] = 1.0
+        got = run_fused(x, w, qtype)
+        assert np.array_equal(got.view(np.uint32), want[:, sel].T.copy().view(np.uint32)), qtype.name
+    # and one at a time through the batch-1 path
+    for c in (0, 33, k - 1):
+        x = np.zeros((1, k), dtype=np.float32)
+        x[0, c] = 1.0
+        got = run_fused(x, w, qtype)
+        assert np.array_equal(got[0].view(np.uint32), want[:, c].copy().view(np.uint32)), (qtype.name, c)
+
+
+@pytest.mark.parametrize("qtype", [QT.Q4_K, QT.Q6_K, QT.IQ2_XS], ids=lambda t: t.name)
+def test_more_rows_than_resident_warps_and_short_rows(qtype):
+    for n, k in ((20_000, 256), (3, 256), (1, 512), (4100, 1024)):
+        w = synth.make_weight_bytes(n, k, qtype, seed=n)
+        x = synth.make_x(2, k, seed=n)
+        check_close(run_fused(x, w, qtype), O.c_matmul(O.bf16_bits(x), w, qtype))
+
+
+def test_leading_dims_and_router():
+    w = synth.make_weight(128, 512, QT.Q4_K, seed=1)
+    x = to_x(synth.make_x(6, 512, seed=1)).reshape(2, 3, 512)
+    y = gj.matmul(x, w)
+    assert y.shape == (2, 3, 128) and y.dtype == torch.bfloat16
+    ref = O.c_matmul(O.bf16_bits(x.reshape(6, 512).float().cpu().numpy()), w.data.cpu().numpy(), QT.Q4_K)
+    check_close(y.reshape(6, 128).float().cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("qtype", REFERENCE_FUSED, ids=lambda t: t.name)
+@pytest.mark.parametrize("m", [1, 8, 64, 512])
+def test_dispatch_agrees_with_fallback(qtype, m):
+    """matmul (fused where it applies) == dequant_matmul, to the tolerance of the reference's
+    tests/test_matmul.py:177-189."""
+    w = synth.make_weight(128, 512, qtype, seed=m)
+    x = to_x(synth.make_x(m, 512, seed=m))
+    got = gj.matmul(x, w).float().cpu().numpy()
+    want = gj.dequant_matmul(x, w).float().cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-2 * np.abs(want).max())
+
+
+@pytest.mark.parametrize("m", [1, 4, 512])
+def test_dequant_matmul_matches_plain(m):
+    w = synth.make_weight(128, 512, QT.Q4_K, seed=m)
+    x = to_x(synth.make_x(m, 512, seed=m))
+    got = gj.dequant_matmul(x, w).double().cpu().numpy()
+    wd = w.dequantize(torch.bfloat16).double().cpu().numpy()
+    ref = x.double().cpu().numpy() @ wd.T
+    np.testing.assert_allclose(got, ref, rtol=2e-2, atol=2e-2 * np.abs(ref).max())
+
+
+def test_blocking_does_not_change_the_result():
+    w = synth.make_weight(128, 512, QT.Q6_K, seed=3)
+    x = to_x(synth.make_x(5, 512, seed=3))
+    whole = gj.dequant_matmul(x, w)
+    split = gj.dequant_matmul(x, w, block_bytes=4 * 16 * 512)
+    assert mm._block_count(128, 512, 4 * 16 * 512) == 8
+    assert torch.equal(whole, split)
+
+
+def test_f32_x_takes_the_fallback():
+    w = synth.make_weight(64, 512, QT.Q4_K, seed=9)
+    x = torch.from_numpy(synth.make_x(2, 512, seed=9)).cuda()
+    y = gj.matmul(x, w)
+    assert y.dtype == torch.float32          # promoted, i.e. not the bf16 fused kernel
+    with pytest.raises(ValueError):
+        kernels.fused_matmul(x, w)
+
+
+def test_gradient_in_x():
+    w = synth.make_weight(64, 512, QT.Q4_K, seed=4)
+    for blocks_bytes in (None, 4 * 16 * 512):
+        x = to_x(synth.make_x(3, 512, seed=4)).requires_grad_(True)
+        y = gj.matmul(x, w, block_bytes=blocks_bytes)
+        g = torch.ones_like(y)
+        y.backward(g)
+        assert x.grad.dtype == x.dtype and x.grad.shape == x.shape
+        W = w.dequantize(torch.float32)
+        want = (g.float() @ W)
+        np.testing.assert_allclose(x.grad.float().cpu().numpy(), want.cpu().numpy(), rtol=2e-2,
+                                   atol=2e-2 * float(want.abs().max()))
+
+
+def test_status_word_is_clean():
+    import ctypes
+    from gguf_jax_b200 import _lib
+    v = ctypes.c_int32(-1)
+    assert _lib.lib().ggq_read_status(torch.cuda.current_device(), ctypes.byref(v)) == 0
+    assert v.value == 0
