@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Headline benchmark: fused Q4_K GEMV on an 8192 x 28672 weight at batch 1.
+
+One *step* is one fused multiply ``y = x @ W.T`` of a bf16 activation row against one
+Q4_K weight (132 MB of blocks).  Steps rotate over several distinct weight copies whose
+total size is a multiple of the 126 MB L2, so every step streams its weight from HBM.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 (launched under torchrun, one rank per GPU): the weight's output rows are sharded
+across the ranks, every rank multiplies its slice and an NCCL all-gather rebuilds the
+replicated ``y`` -- total work is fixed, so scaling is "strong".
+
+Rank 0 prints ONE JSON line.  Keys beyond the common contract:
+  roofline     achieved = algorithmic bytes of one launch / mean launch time (CUDA events
+               around the timed region, on the launching stream); peak = measured copy
+               bandwidth from MEASURED_PEAKS.json (fallback 6650 GB/s, marked as such).
+  cpu_baseline the CPU restatement of the same multiply (oracle/, OpenMP) timed on this
+               host on a bounded row sample of the same weight.
+  e2e          the same multiply through the public API (gguf_jax_b200.matmul) with the
+               activation coming from pinned host memory and the result read back to the
+               host inside the timed region; the weight stays resident on the device, as in
+               the reference, where parameters live on the device and only activations move.
+
+``--impl reference`` times the reference's CPU route (dequantize + multiply, restated in
+oracle/ because JAX is not installed here) with all host threads on a bounded row sample
+per step, and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_ROWS, K_DIM, BATCH = 8192, 28672, 1
+QTYPE_NAME = "Q4_K"
+METRIC = "q4_k_fused_gemv_hbm_throughput"
+UNIT = "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from
+# the ncu capture summarised under profiles/ (None until captured).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_SOURCE = None
+
+
+def algorithmic_bytes(n: int, k: int, m: int, out_itemsize: int = 2) -> int:
+    """Quantized weight + activations + output: the bytes one launch must move."""
+    return n * (k // 256) * 144 + 2 * m * k + out_itemsize * m * n
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:  # noqa: BLE001
+        return 6650.0, "fallback (6650 GB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.gpu), "-lms", "200"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:  # noqa: BLE001
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:  # noqa: BLE001
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                p = [s.strip() for s in line.split(",")]
+                if len(p) < 9:
+                    continue
+                sm.append(float(p[1]))
+                mx.append(float(p[2]))
+                for name, val in zip(names, p[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:  # noqa: BLE001
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline(seconds: float = 10.0, rows: int = 1024) -> dict:
+    """The CPU restatement (oracle/, OpenMP, float32) on a bounded row sample."""
+    import numpy as np
+    from gguf.constants import GGMLQuantizationType as QT
+
+    from gguf_jax_b200 import synth
+    from oracle import oracle as O
+
+    qt = QT[QTYPE_NAME]
+    w = synth.make_weight_bytes(rows, K_DIM, qt, seed=0)
+    x = O.bf16_bits(synth.make_x(BATCH, K_DIM, seed=0))
+    O.c_matmul(x, w[:64], qt, plain_f32=True)  # warm up threads / page in
+    t0 = time.perf_counter()
+    passes = 0
+    while True:
+        O.c_matmul(x, w, qt, plain_f32=True)
+        passes += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds or passes >= 100000:
+            break
+    per_pass = algorithmic_bytes(rows, K_DIM, BATCH, 4)
+    return {"value": per_pass * passes / dt / 1e9, "unit": UNIT, "cores": O.threads(), "kind": "port",
+            "sample": f"{passes} passes over {rows} of {N_ROWS} rows of the same Q4_K weight "
+                      f"(K={K_DIM}, batch {BATCH}) in {dt:.1f} s; fused decode+dot, float32, OpenMP"}
+
+
+def run_reference(args) -> None:
+    """--impl reference: the CPU route on this host's cores; rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import numpy as np  # noqa: F401
+    from gguf.constants import GGMLQuantizationType as QT
+
+    from gguf_jax_b200 import synth
+    from oracle import oracle as O
+
+    qt = QT[QTYPE_NAME]
+    rows = 512
+    w = synth.make_weight_bytes(rows, K_DIM, qt, seed=0)
+    x = O.bf16_bits(synth.make_x(BATCH, K_DIM, seed=0))
+    for _ in range(args.warmup):
+        O.c_matmul(x, w, qt, plain_f32=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.c_matmul(x, w, qt, plain_f32=True)
+    dt = time.perf_counter() - t0
+    value = algorithmic_bytes(rows, K_DIM, BATCH, 4) * args.steps / dt / 1e9
+    sample = (f"each step = {rows} of {N_ROWS} rows of the Q4_K weight (K={K_DIM}, batch {BATCH}); "
+              "CPU restatement of dequantize + multiply (oracle/, OpenMP) because JAX is not installed")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"Q4_K fused GEMV {N_ROWS}x{K_DIM} batch {BATCH}", "sample_rows": rows},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": O.threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from gguf.constants import GGMLQuantizationType as QT
+
+    import gguf_jax_b200 as gj
+    from gguf_jax_b200 import _lib, kernels, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()
+    qt = QT[QTYPE_NAME]
+
+    rows_local = N_ROWS // world
+    assert rows_local * world == N_ROWS
+    copies = 4  # 4 x 132 MB = 528 MB of distinct weights, > 4x the 126 MB L2
+    weights = []
+    for c in range(copies):
+        full = synth.make_weight_on_device(N_ROWS, K_DIM, qt, seed=c, device=dev)
+        shard = full.data[rank * rows_local:(rank + 1) * rows_local].contiguous()
+        weights.append(gj.QuantizedArray(shard, qt, (rows_local, K_DIM)))
+        del full
+    x = torch.from_numpy(synth.make_x(BATCH, K_DIM, seed=0)).to(dev).to(torch.bfloat16)
+    y_local = [None]
+    y_full = torch.empty((world, BATCH, rows_local), dtype=torch.bfloat16, device=dev) if world > 1 else None
+
+    def step(i: int):
+        y = kernels.fused_matmul(x, weights[i % copies])
+        if world > 1:
+            dist.all_gather_into_tensor(y_full, y)
+        y_local[0] = y
+
+    stream = torch.cuda.Stream(dev)
+    launches_per_step = 1
+    with torch.cuda.stream(stream):
+        for i in range(max(args.warmup, 3)):
+            step(i)
+        stream.synchronize()
+        # one CUDA graph of `steps` launches: the Python/ctypes launch cost would otherwise
+        # exceed the ~20 us kernel
+        graph = None
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(args.steps):
+                    step(i)
+        except Exception as e:  # noqa: BLE001
+            graph = None
+            if rank == 0:
+                print(f"[bench] graph capture unavailable ({type(e).__name__}: {e}); timing eager launches",
+                      file=sys.stderr)
+    torch.cuda.synchronize()
+
+    def timed_region() -> float:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            if graph is not None:
+                graph.replay()
+            else:
+                for i in range(args.steps):
+                    step(i)
+            e1.record(stream)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    timed_region()  # one untimed replay so the graph itself is warm
+    with ClockSampler(local_rank) as clocks:
+        t_start = time.perf_counter()
+        ms = timed_region()
+        # keep sampling for at least ~1 s of the same load so the clock record has samples
+        extra = []
+        while time.perf_counter() - t_start < 1.2:
+            extra.append(timed_region())
+    clk = clocks.summary()
+    ms_all = [ms] + extra
+    ms = statistics.median(ms_all)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    total_bytes = algorithmic_bytes(N_ROWS, K_DIM, BATCH) * args.steps
+    value = total_bytes / (ms * 1e-3) / 1e9
+    launch_bytes = algorithmic_bytes(rows_local, K_DIM, BATCH)
+    launch_ms = ms / args.steps
+    peak, peak_src = measured_peak()
+    achieved = launch_bytes / (launch_ms * 1e-3) / 1e9
+
+    # end to end through the public API: activation from pinned host memory, result to host
+    xh = x.cpu().pin_memory()
+    yh = torch.empty((BATCH, N_ROWS), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = min(args.steps, 200)
+
+    def e2e_step(i: int):
+        xd = xh.to(dev, non_blocking=True)
+        y = gj.matmul(xd, weights[i % copies])
+        if world > 1:
+            dist.all_gather_into_tensor(y_full, y)
+            yh.view(world, BATCH, rows_local).copy_(y_full, non_blocking=True)
+        else:
+            yh.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = algorithmic_bytes(N_ROWS, K_DIM, BATCH) * e2e_steps / e2e_s / 1e9
+
+    if rank == 0:
+        cpu = cpu_baseline() if world == 1 else None
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": launch_ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {
+                "workload": f"Q4_K fused GEMV {N_ROWS}x{K_DIM} batch {BATCH} (bf16 x, bf16 y)",
+                "rows_per_gpu": rows_local, "parallelism": f"row-sharded x{world} + all-gather" if world > 1 else "1 GPU",
+                "l2_policy": f"inputs larger than L2: steps rotate over {copies} distinct weights "
+                             f"({copies * algorithmic_bytes(N_ROWS, K_DIM, 0) / 1e6:.0f} MB)",
+                "timing": "CUDA events around one CUDA graph of all steps" if graph is not None else "CUDA events around eager launches",
+                "repeats": len(ms_all),
+            },
+            "roofline": {
+                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "peak_source": peak_src,
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "traffic_source": NCU_TRAFFIC_SOURCE,
+                "algorithmic_bytes_per_launch": launch_bytes, "launch_us": launch_ms * 1e3,
+            },
+            "clocks": clk,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * BATCH * K_DIM,
+                    "d2h_bytes_per_step": 2 * BATCH * N_ROWS, "steps": e2e_steps,
+                    "ms_per_step": e2e_s / e2e_steps * 1e3,
+                    "note": "weight resident on the device; activation H2D from pinned memory and result D2H every step"},
+            "gpu_launches": args.steps * launches_per_step,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
