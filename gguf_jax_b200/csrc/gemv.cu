@@ -15,15 +15,22 @@ extern "C" int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K) {
   return kGemvMaxBatch;
 }
 
+static int sm_count_of(int dev) {
+  static int cached[64] = {};
+  if (dev < 0 || dev >= 64) return 0;
+  if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+  return cached[dev];
+}
+
 extern "C" size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32_t M) {
-  (void)qtype; (void)N; (void)K; (void)M;
+  (void)K; (void)M;
+  if (qtype == QT_Q4_K && N > 0) return gemv_q4k_workspace_bytes(N, kMaxSmCount);
   return 0;
 }
 
 extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
                             int32_t M, void* y, int32_t y_dtype, void* workspace, size_t workspace_bytes,
                             void* stream) {
-  (void)workspace; (void)workspace_bytes;
   const TypeInfo* ti = type_info(qtype);
   if (!ti) return fail(GGQ_BAD_QTYPE, "ggq_gemv: qtype %d is not decodable", qtype);
   if (!ti->fused) return fail(GGQ_UNSUPPORTED, "ggq_gemv: no fused kernel for qtype %d", qtype);
@@ -42,7 +49,15 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
   if (ti->needs_tables && !tab)
     return fail(GGQ_NO_TABLES, "ggq_gemv: call ggq_set_tables(%d, ...) before using qtype %d", dev, qtype);
   cudaStream_t st = (cudaStream_t)stream;
-  cudaError_t err = gemv_generic(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, st);
+  cudaError_t err;
+  if (qtype == QT_Q4_K && gemv_q4k_applicable(N, K, M, w, x_bf16) && workspace &&
+      workspace_bytes >= gemv_q4k_workspace_bytes(N, kMaxSmCount) && (uintptr_t)workspace % 256 == 0 &&
+      sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount) {
+    err = gemv_q4k((const uint8_t*)w, N, K, x_bf16, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev),
+                   device_status_word(dev), st);
+  } else {
+    err = gemv_generic(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, st);
+  }
   if (err != cudaSuccess) return fail(GGQ_LAUNCH_FAILED, "ggq_gemv: %s", cudaGetErrorString(err));
   return GGQ_OK;
 }

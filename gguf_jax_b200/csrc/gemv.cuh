@@ -16,4 +16,13 @@ __device__ __forceinline__ void store_out(void* y, int y_dtype, int64_t idx, flo
 cudaError_t gemv_generic(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K, const void* x, int M,
                          void* y, int y_dtype, const uint8_t* tab, cudaStream_t st);
 
+// Q4_K, batch 1: TMA-staged tensor-core kernel (gemv_q4k.cu).
+bool gemv_q4k_applicable(int64_t N, int64_t K, int M, const void* w, const void* x);
+size_t gemv_q4k_workspace_bytes(int64_t N, int sm_count);
+cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void* y, int y_dtype, void* ws,
+                     size_t ws_bytes, int sm_count, int* status, cudaStream_t st);
+
+// Upper bound on the SM count used when sizing scratch (the kernels use the real count).
+constexpr int kMaxSmCount = 256;
+
 }  // namespace ggq

@@ -169,3 +169,33 @@ def test_status_word_is_clean():
     v = ctypes.c_int32(-1)
     assert _lib.lib().ggq_read_status(torch.cuda.current_device(), ctypes.byref(v)) == 0
     assert v.value == 0
+
+
+# ---- the tuned Q4_K batch-1 kernel (TMA ring + tensor-core dot products + split-K finish) ----
+
+@pytest.mark.parametrize("n,k", [(1, 256), (3, 512), (33, 9 * 256), (200, 11 * 256), (4100, 1024), (20_000, 256),
+                                 (8192, 2048), (512, 28672), (1024, 8192), (148 * 32, 4096), (5000, 7 * 256)])
+def test_q4k_batch1_kernel_shapes(n, k):
+    w = synth.make_weight_bytes(n, k, QT.Q4_K, seed=n + k)
+    x = synth.make_x(1, k, seed=n)
+    ref = O.c_matmul(O.bf16_bits(x), w, QT.Q4_K)
+    got32 = run_fused(x, w, QT.Q4_K, torch.float32)
+    assert O.rel_l2(got32, ref) <= 2e-5, (n, k, O.rel_l2(got32, ref))
+    got16 = run_fused(x, w, QT.Q4_K)
+    assert np.array_equal(got16, torch.from_numpy(got32).to(torch.bfloat16).float().numpy())
+    check_close(got16, ref)
+
+
+def test_q4k_batch1_kernel_is_deterministic_and_leaves_scratch_clean():
+    shapes = [(8192, 2048), (200, 11 * 256), (4100, 1024)]
+    first = {}
+    for rep in range(3):
+        for n, k in shapes:
+            w = synth.make_weight_bytes(n, k, QT.Q4_K, seed=1)
+            x = synth.make_x(1, k, seed=2)
+            got = run_fused(x, w, QT.Q4_K, torch.float32)
+            if rep == 0:
+                first[(n, k)] = got
+                assert O.rel_l2(got, O.c_matmul(O.bf16_bits(x), w, QT.Q4_K)) <= 2e-5
+            else:
+                assert np.array_equal(got.view(np.uint32), first[(n, k)].view(np.uint32))
