@@ -216,6 +216,15 @@ def run_ours(args) -> None:
             dist.all_gather_into_tensor(y_full, y)
         y_local[0] = y
 
+    if args.profile:
+        for i in range(args.warmup + args.steps):
+            step(i)
+        torch.cuda.synchronize()
+        print(f"profile run: {args.warmup + args.steps} eager launches done", file=sys.stderr)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     stream = torch.cuda.Stream(dev)
     launches_per_step = 1
     with torch.cuda.stream(stream):
@@ -350,6 +359,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile", action="store_true",
+                    help="profiler-friendly run: a few eager launches of the hot kernel, no graph, "
+                         "no CPU baseline, no end-to-end leg, no JSON line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
