@@ -12,12 +12,13 @@ import threading
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libggq_b200.so")
+# GGQ_B200_LIB overrides the in-tree library (for trying out a differently built copy).
+LIB_PATH = os.environ.get("GGQ_B200_LIB") or os.path.join(_HERE, "libggq_b200.so")
 
 GGQ_F32, GGQ_BF16, GGQ_F16 = 0, 1, 2
 
 _lib = None
-_lock = threading.Lock()
+_lock = threading.RLock()  # ensure_tables() calls lib() while holding it
 _tables_done: set[int] = set()
 
 # name -> (restype, argtypes); one entry per declaration in include/ggq.h

@@ -1,14 +1,17 @@
 // Q4_K fused decode + multiply for batch 1, tuned for B200 HBM bandwidth.
 //
 // Data movement.  A persistent CTA per SM with sixteen warps.  Every warp streams its own
-// tiles (16 weight rows x one 144-byte superblock) straight from HBM into registers with
-// 128-bit read-only loads, one tile ahead of the one it is multiplying; the sixteen warps
-// of a CTA sit on adjacent superblocks of the same 32 rows, so each row is read as a
-// contiguous run.  Plain loads are used rather than TMA on purpose: measured on this part, a
-// ring fed by cp.async.bulk copies of ~1 KB per row stops at 3.4 TB/s (about 50 cycles of
-// fixed cost per bulk copy, one TMA unit per SM), copies of 16 KB reach 5.7 TB/s, while
-// 128-bit loads issued by all warps stream 5.8-6.4 TB/s.  The GGUF row-major block layout
-// only offers ~1 KB contiguous per row per 16-row tile, so the loads win.
+// tiles (16 weight rows x one 144-byte superblock, 2304 B) from HBM into a private ring of
+// shared-memory slots with 16-byte cp.async copies, three tiles ahead of the one it is
+// multiplying (about 110 KB in flight per SM, no registers held by loads in flight); the
+// sixteen warps of a CTA sit on adjacent superblocks of the same 32 rows, so each row is
+// read as a contiguous run.  Per-thread cp.async is used rather than TMA on purpose:
+// measured on this part, a ring fed by cp.async.bulk copies of ~1 KB per row stops at
+// 3.4 TB/s (about 50 cycles of fixed cost per bulk copy, one TMA unit per SM) and copies of
+// 16 KB reach 5.7 TB/s, while 16-byte loads issued by all warps stream 5.8-6.4 TB/s.  The
+// GGUF row-major block layout only offers ~1 KB contiguous per row per 16-row tile, so the
+// per-thread copies win.  A tile is stored densely (row pitch 144 B = 16 mod 128), which
+// makes the 128-bit shared-memory reads of the MMA fragment layout bank-conflict free.
 //
 // Arithmetic.  Per-element FMAs cannot keep up with HBM on this part (about 2.5 issued
 // lane-instructions per weight at peak bandwidth), so the dot products run on the tensor
@@ -48,19 +51,26 @@ namespace ggq {
 namespace q4k {
 
 constexpr int kBlockBytes = 144;
-constexpr int kWarps = 16;
+constexpr int kRowTiles = 2;                   // 16-row tiles per unit
+constexpr int kWarps = 8 * kRowTiles;          // one warp per (row tile, superblock pair of the chunk)
 constexpr int kThreads = kWarps * 32;
-constexpr int kRowsPerUnit = 32;
-constexpr int kSbPerUnit = 8;
-constexpr int kMaxK = 98304;   // bf16 activations (2 B each) + their sums stay resident in shared memory
+constexpr int kRowsPerUnit = 16 * kRowTiles;
+constexpr int kSbPerWarp = 2;                  // adjacent superblocks a warp multiplies per step (288 B per row)
+constexpr int kSbPerUnit = 8 * kSbPerWarp;
+constexpr int kTileBytes = 16 * kBlockBytes;   // 2304
+constexpr int kSlotPitch = kSbPerWarp * kBlockBytes + 16;   // 304 = 48 (mod 128): conflict-free 128-bit reads
+constexpr int kSlotBytes = 16 * kSlotPitch;                // one warp's step: 16 rows x 288 B (+ 16 B pad)
+constexpr int kSmemLimit = 232448;             // 227 KB opt-in limit per CTA
 
 struct Smem {
-  static constexpr int x = 0;                                                   // bf16[K], scaled + permuted
-  static __host__ __device__ constexpr int xs(int K) { return x + 2 * K; }       // float[K/32] sub-block sums
-  static __host__ __device__ constexpr int zero(int K) { return xs(K) + (K / 32) * 4; }  // 64 zero bytes
-  static __host__ __device__ constexpr int red(int K) { return zero(K) + 64; }   // float[2][16 warps][16]
-  static __host__ __device__ constexpr int misc(int K) { return red(K) + 2 * kWarps * 16 * 4; }
-  static __host__ __device__ constexpr int total(int K) { return misc(K) + 16; }
+  // ring: [16 warps][DEPTH slots][2304 B] precedes everything else
+  int x;                                                                         // bf16[K], scaled + permuted
+  __host__ __device__ explicit Smem(int depth) : x(kWarps * depth * kSlotBytes) {}
+  __host__ __device__ int xs(int K) const { return x + 2 * K; }       // float[K/32] sub-block sums
+  __host__ __device__ int zero(int K) const { return xs(K) + (K / 32) * 4; }  // 64 zero bytes
+  __host__ __device__ int red(int K) const { return zero(K) + 64; }   // float[2][kWarps][16]
+  __host__ __device__ int misc(int K) const { return red(K) + 2 * kWarps * 16 * 4; }
+  __host__ __device__ int total(int K) const { return misc(K) + 16; }
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -69,13 +79,12 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
-// Streaming 128-bit load: read-only path, no L1 allocation priority (each byte is used once).
-__device__ __forceinline__ uint4 ldg_stream(const uint8_t* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
+__device__ __forceinline__ void cp_async16(uint32_t dst, const uint8_t* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -83,66 +92,72 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// x >> S computed as the high word of x * 2^(32-S): an integer multiply-add (FMA pipe) instead
+// of a shift (ALU pipe, half rate and the busiest pipe of this kernel).
+template <int S>
+__device__ __forceinline__ uint32_t shr_fma(uint32_t x) {
+  uint32_t r;
+  asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(1u << (32 - S)));
+  return r;
+}
+// byte `SEL` (0..3) of x as a float, exact: bits 0x4B0000vv are 2^23 + v.
+template <int SEL>
+__device__ __forceinline__ float byte_to_float(uint32_t x) {
+  return __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7440 + SEL)) - 8388608.0f;
+}
 __device__ __forceinline__ float bf16lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
 
 // Which CTA owns unit u when U units are dealt to G CTAs as ranges [U*b/G, U*(b+1)/G).
 __device__ __forceinline__ int owner_of(int64_t u, int64_t U, int G) { return (int)(((u + 1) * G - 1) / U); }
 
-// Scales of the sub-block pair (2t, 2t+1) from a block header (d|dmin, s0-3, s4-7, s8-11):
-// dl = d * sc, dm = dmin * mn, the products exact in float32 (src/gguf_jax/quants.py:275-305).
-// d is additionally multiplied by the power of two `d_up` that undoes the activation scaling.
-__device__ __forceinline__ void pair_scales(const uint4& h, int t, float d_up, float& dl_a, float& dm_a,
-                                            float& dl_b, float& dm_b) {
-  const __half2 dd = *reinterpret_cast<const __half2*>(&h.x);
-  const float d = __fmul_rn(__low2float(dd), d_up), dmin = __high2float(dd);
-  const int sh = 16 * (t & 1);
-  const uint32_t u1 = h.y >> sh, u2 = h.z >> sh, u3 = h.w >> sh;
-  uint32_t scp, mnp;
-  if (t < 2) {
-    scp = u1 & 0x3F3Fu;
-    mnp = u2 & 0x3F3Fu;
-  } else {
-    scp = (u3 & 0x0F0Fu) | ((u1 >> 2) & 0x3030u);
-    mnp = ((u3 >> 4) & 0x0F0Fu) | ((u2 >> 2) & 0x3030u);
-  }
-  dl_a = __fmul_rn(d, (float)(scp & 0xFF));
-  dl_b = __fmul_rn(d, (float)(scp >> 8));
-  dm_a = __fmul_rn(dmin, (float)(mnp & 0xFF));
-  dm_b = __fmul_rn(dmin, (float)(mnp >> 8));
-}
-
-// One lane's share of a tile: block header and 32 quant bytes of rows g and g+8.
-struct TileRegs {
-  uint4 h0, h1, qa0, qb0, qa1, qb1;
+// Per-lane constants of the 6-bit scale unpack: lanes t < 2 own sub-blocks 0..3 (plain 6-bit
+// fields), lanes t >= 2 own sub-blocks 4..7 (4 low bits in bytes 8..11, 2 high bits on top of
+// bytes 0..7).  Written with selects and masks so the unpack is branch-free.
+struct LaneScale {
+  bool low;          // t < 2
+  int sh, sh2, shm;  // 16 (t & 1), sh + 2, sh + (low ? 0 : 4)
+  uint32_t ma, mb;   // 0x3F3F / 0 for low lanes, 0x0F0F / 0x3030 otherwise
+  __device__ explicit LaneScale(int t)
+      : low(t < 2), sh(16 * (t & 1)), sh2(16 * (t & 1) + 2), shm(16 * (t & 1) + (t < 2 ? 0 : 4)),
+        ma(t < 2 ? 0x3F3Fu : 0x0F0Fu), mb(t < 2 ? 0u : 0x3030u) {}
 };
 
-__device__ __forceinline__ void load_tile(TileRegs& r, const uint8_t* p0, const uint8_t* p1, int t) {
-  r.h0 = ldg_stream(p0);
-  r.h1 = ldg_stream(p1);
-  r.qa0 = ldg_stream(p0 + 16 + 32 * t);
-  r.qb0 = ldg_stream(p0 + 32 + 32 * t);
-  r.qa1 = ldg_stream(p1 + 16 + 32 * t);
-  r.qb1 = ldg_stream(p1 + 32 + 32 * t);
+// Scales of the sub-block pair (2t, 2t+1) from a block header (d|dmin, s0-3, s4-7, s8-11):
+// dl = d * sc, ndm = -(dmin * mn), the products exact in float32 (src/gguf_jax/quants.py:275-305).
+__device__ __forceinline__ void pair_scales(const uint4& h, const LaneScale& c, float& dl_a, float& ndm_a,
+                                            float& dl_b, float& ndm_b) {
+  const __half2 dd = *reinterpret_cast<const __half2*>(&h.x);
+  const float d = __low2float(dd), ndmin = -__high2float(dd);
+  const uint32_t a_sc = c.low ? h.y : h.w, a_mn = c.low ? h.z : h.w;
+  const uint32_t scp = ((a_sc >> c.sh) & c.ma) | ((h.y >> c.sh2) & c.mb);
+  const uint32_t mnp = ((a_mn >> c.shm) & c.ma) | ((h.z >> c.sh2) & c.mb);
+  dl_a = __fmul_rn(d, byte_to_float<0>(scp));
+  dl_b = __fmul_rn(d, byte_to_float<1>(scp));
+  ndm_a = __fmul_rn(ndmin, byte_to_float<0>(mnp));
+  ndm_b = __fmul_rn(ndmin, byte_to_float<1>(mnp));
 }
 
-// Multiply one tile by the activations of superblock `sbg` and add this lane's share of the
+// Multiply one tile by its superblock's activations (at xa, sums at xsa) and add this lane's share of the
 // 16 row sums to out0 (row g) / out1 (row g+8).
-__device__ __forceinline__ void compute_tile(const TileRegs& r, int sbg, int g, int t, bool live, uint32_t x_base,
-                                             uint32_t zero_base, const float* xs, float d_up, float& out0,
-                                             float& out1) {
+__device__ __forceinline__ void compute_tile(uint32_t tile, int g, int t, const LaneScale& lc, uint32_t xa,
+                                             uint32_t x_step, uint32_t xsa, float& out0, float& out1) {
+  // this lane's share of the tile: block header and 32 quant bytes of rows g and g+8
+  const uint32_t base0 = tile + g * kSlotPitch, base1 = base0 + 8 * kSlotPitch;
+  const uint4 h0 = lds128(base0), h1 = lds128(base1);
+  const uint4 qa0 = lds128(base0 + 16 + 32 * t), qb0 = lds128(base0 + 32 + 32 * t);
+  const uint4 qa1 = lds128(base1 + 16 + 32 * t), qb1 = lds128(base1 + 32 + 32 * t);
   // A lane feeds column g of the B operand; that column is live only in the k-slots of lane
-  // group g/2, so every other lane reads zeros.
-  const uint32_t xa = live ? x_base + (uint32_t)(sbg * 8 + g) * 64 : zero_base;
-  const uint32_t xstep = live ? 16u : 0u;
-  const uint4 x0 = lds128(xa), x1 = lds128(xa + xstep), x2 = lds128(xa + 2 * xstep), x3 = lds128(xa + 3 * xstep);
-  const float2 sx = *reinterpret_cast<const float2*>(xs + sbg * 8 + 2 * t);   // X[2t], X[2t+1]
+  // group g/2, so every other lane reads the zero page (base = zero page, strides = 0).
+  const uint4 x0 = lds128(xa), x1 = lds128(xa + x_step), x2 = lds128(xa + 2 * x_step), x3 = lds128(xa + 3 * x_step);
+  float2 sx;   // X[2t], X[2t+1], already scaled like the accumulators
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(sx.x), "=f"(sx.y) : "r"(xsa));
 
   // Two accumulator tiles: the low-nibble pass and the high-nibble pass both multiply by this
   // lane's activations; only column 2t of the first and 2t+1 of the second are kept.
   float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
-  const uint32_t w0[8] = {r.qa0.x, r.qa0.y, r.qa0.z, r.qa0.w, r.qb0.x, r.qb0.y, r.qb0.z, r.qb0.w};
-  const uint32_t w1[8] = {r.qa1.x, r.qa1.y, r.qa1.z, r.qa1.w, r.qb1.x, r.qb1.y, r.qb1.z, r.qb1.w};
+  const uint32_t w0[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qb0.x, qb0.y, qb0.z, qb0.w};
+  const uint32_t w1[8] = {qa1.x, qa1.y, qa1.z, qa1.w, qb1.x, qb1.y, qb1.z, qb1.w};
   const uint32_t xr[16] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w,
                            x2.x, x2.y, x2.z, x2.w, x3.x, x3.y, x3.z, x3.w};
 #pragma unroll
@@ -151,65 +166,99 @@ __device__ __forceinline__ void compute_tile(const TileRegs& r, int sbg, int g, 
     // nibbles) and 2t+1 (high nibbles).  Bytes (0,2) fill k-slots 2t,2t+1; bytes (1,3) fill
     // k-slots 2t+8,2t+9, matching the pair-permuted activations.
     const uint32_t a = w0[i], b = w1[i];
-    const uint32_t as = a >> 8, bs = b >> 8;
+    const uint32_t as = shr_fma<8>(a), bs = shr_fma<8>(b);
     mma16816(lo, a & 0x000F000Fu, b & 0x000F000Fu, as & 0x000F000Fu, bs & 0x000F000Fu, xr[2 * i], xr[2 * i + 1]);
     mma16816(hi, a & 0x00F000F0u, b & 0x00F000F0u, as & 0x00F000F0u, bs & 0x00F000F0u, xr[2 * i], xr[2 * i + 1]);
   }
   float dla, dma, dlb, dmb;
-  pair_scales(r.h0, t, d_up, dla, dma, dlb, dmb);
-  out0 = fmaf(dla, lo[0], out0); out0 = fmaf(-dma, sx.x, out0);
-  out0 = fmaf(dlb, hi[1], out0); out0 = fmaf(-dmb, sx.y, out0);
-  pair_scales(r.h1, t, d_up, dla, dma, dlb, dmb);
-  out1 = fmaf(dla, lo[2], out1); out1 = fmaf(-dma, sx.x, out1);
-  out1 = fmaf(dlb, hi[3], out1); out1 = fmaf(-dmb, sx.y, out1);
+  pair_scales(h0, lc, dla, dma, dlb, dmb);
+  out0 = fmaf(dla, lo[0], out0); out0 = fmaf(dma, sx.x, out0);
+  out0 = fmaf(dlb, hi[1], out0); out0 = fmaf(dmb, sx.y, out0);
+  pair_scales(h1, lc, dla, dma, dlb, dmb);
+  out1 = fmaf(dla, lo[2], out1); out1 = fmaf(dma, sx.x, out1);
+  out1 = fmaf(dlb, hi[3], out1); out1 = fmaf(dmb, sx.y, out1);
 }
 
+template <int DEPTH>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat16* __restrict__ x,
                    void* __restrict__ y, int y_dtype, int* __restrict__ counters, float* __restrict__ partials) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int SB = K / 256;                        // superblocks per row
-  const int64_t row_bytes = (int64_t)SB * kBlockBytes;
+  const int row_bytes = SB * kBlockBytes;
   const int C = (SB + kSbPerUnit - 1) / kSbPerUnit;   // chunks per row group
   const int RG = (N + kRowsPerUnit - 1) / kRowsPerUnit;
   const int64_t U = (int64_t)RG * C;
   const int G = gridDim.x, b = blockIdx.x;
   const int64_t u_begin = U * b / G, u_end = U * (b + 1) / G;
   const int n_units = (int)(u_end - u_begin);
+  const int rg_begin = (int)(u_begin / C), c_begin = (int)(u_begin - (int64_t)rg_begin * C);
 
   const int g = lane >> 2, t = lane & 3;
   const int rt = warp >> 3, j = warp & 7;        // row tile (16 rows) and superblock slot of this warp
-  int rg = (int)(u_begin / C), c = (int)(u_begin - (int64_t)(u_begin / C) * C);
 
-  // Address of this lane's rows for a unit; rows past N are clamped (loaded, never stored).
-  auto tile_ptrs = [&](int rg_, int c_, const uint8_t*& p0, const uint8_t*& p1) -> bool {
-    const int sbg = c_ * kSbPerUnit + j;
-    const int r0 = min(rg_ * kRowsPerUnit + 16 * rt + g, N - 1), r1 = min(rg_ * kRowsPerUnit + 16 * rt + g + 8, N - 1);
-    const int sbc = min(sbg, SB - 1);
-    p0 = w + (int64_t)r0 * row_bytes + (int64_t)sbc * kBlockBytes;
-    p1 = w + (int64_t)r1 * row_bytes + (int64_t)sbc * kBlockBytes;
-    return sbg < SB;
+  const Smem L(DEPTH);
+  const uint32_t my_ring = smem_u32(smem) + warp * (DEPTH * kSlotBytes);
+
+  // ---- copy side.  A step's slot holds 16 rows x 288 B (two adjacent superblocks per row) at a
+  // row pitch of 304 B.  Nine cp.async instructions fill it: eight copy pieces 0..15 (256 B) of
+  // two rows each (one row per half-warp), the ninth copies pieces 16..17 of all sixteen rows.
+  // Source and destination are affine in the instruction index, so a lane keeps three offsets.
+  // The last row group of a weight whose N is not a multiple of 32 takes a slower path that
+  // clamps every row to N - 1 (copied, multiplied, never stored); a missing second superblock
+  // (odd K/256) is never multiplied, its 144 bytes are simply not copied.
+  const int hl = lane >> 4, kl = lane & 15;
+  const int32_t src_a = hl * row_bytes + 16 * kl, src_b = (lane >> 1) * row_bytes + 256 + 16 * (lane & 1);
+  const uint32_t dst_a = hl * kSlotPitch + 16 * kl, dst_b = (lane >> 1) * kSlotPitch + 256 + 16 * (lane & 1);
+  const uint8_t* src = w;        // first source byte of the next step
+  int rg_i = rg_begin, c_i = c_begin, issued = 0, slot_i = 0;
+  auto seek_row_group = [&]() {
+    src = w + (int64_t)(rg_i * kRowsPerUnit + 16 * rt) * row_bytes +
+          (int64_t)(c_i * kSbPerUnit + kSbPerWarp * j) * kBlockBytes;
   };
+  seek_row_group();
+  auto issue_next = [&]() {
+    if (issued < n_units) {
+      const int sb0 = c_i * kSbPerUnit + kSbPerWarp * j;
+      const uint32_t dst = my_ring + slot_i * kSlotBytes;
+      const int row0 = rg_i * kRowsPerUnit + 16 * rt;
+      if (sb0 + 1 < SB && row0 + 16 <= N) {
+        // common case: both superblocks and all sixteen rows exist
+        const uint8_t* pa = src + src_a;
+#pragma unroll
+        for (int i = 0; i < 8; i++) cp_async16(dst + dst_a + i * (2 * kSlotPitch), pa + (int64_t)i * (2 * row_bytes));
+        cp_async16(dst + dst_b, src + src_b);
+      } else if (sb0 < SB) {
+        const int nsb = min(kSbPerWarp, SB - sb0);
+        for (int p = lane; p < 16 * 9 * nsb; p += 32) {
+          const int row = p / (9 * nsb), k = p - row * (9 * nsb);
+          const int64_t roff = (int64_t)(min(row0 + row, N - 1) - row0) * row_bytes;
+          cp_async16(dst + row * kSlotPitch + 16 * k, src + roff + 16 * k);
+        }
+      }
+      ++issued;
+      if (++slot_i == DEPTH) slot_i = 0;
+      src += kSbPerUnit * kBlockBytes;
+      if (++c_i == C) { c_i = 0; ++rg_i; seek_row_group(); }
+    }
+    cp_async_commit();
+  };
+  // Fill the pipeline before the activation prologue so HBM is busy from the first cycle.
+#pragma unroll
+  for (int d = 0; d < DEPTH - 1; d++) issue_next();
 
-  // Start the first tile's loads before the activation prologue so HBM is busy from cycle one.
-  TileRegs cur, nxt;
-  {
-    const uint8_t *p0, *p1;
-    if (n_units > 0) { tile_ptrs(rg, c, p0, p1); load_tile(cur, p0, p1, t); }
-  }
-
-  float* xs = reinterpret_cast<float*>(smem + Smem::xs(K));
-  int* xmax = reinterpret_cast<int*>(smem + Smem::misc(K));
+  float* xs = reinterpret_cast<float*>(smem + L.xs(K));
+  int* xmax = reinterpret_cast<int*>(smem + L.misc(K));
   int S;  // activations are held as x * 2^S (even sub-blocks) / x * 2^(S-4) (odd sub-blocks)
   {
     // Once per CTA: zero page, per-sub-block sums X, largest |x|, then x written to shared
     // memory as scaled, pair-permuted bf16: word 2i = (x[4i], x[4i+2]), word 2i+1 = (x[4i+1], x[4i+3]).
-    if (tid < 16) reinterpret_cast<uint32_t*>(smem + Smem::zero(K))[tid] = 0;
+    if (tid < 16) reinterpret_cast<uint32_t*>(smem + L.zero(K))[tid] = 0;
     if (tid == 0) *xmax = 0;
     __syncthreads();
     const uint4* xg = reinterpret_cast<const uint4*>(x);
-    uint4* xv = reinterpret_cast<uint4*>(smem + Smem::x);
+    uint4* xv = reinterpret_cast<uint4*>(smem + L.x);
     uint32_t mx = 0;
     for (int sblk = tid; sblk < K / 32; sblk += kThreads) {
       float sum = 0.f;
@@ -230,7 +279,9 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
     S = max(8, min(64, 252 - emax));
     const float up_even = __uint_as_float((uint32_t)(127 + S) << 23);
     const float up_odd = __uint_as_float((uint32_t)(127 + S - 4) << 23);
+    const float xs_scale = __uint_as_float((uint32_t)(127 + S - 133) << 23);   // sums follow the accumulators' scale
     for (int sblk = tid; sblk < K / 32; sblk += kThreads) {
+      xs[sblk] *= xs_scale;
       const float up = (sblk & 1) ? up_odd : up_even;
 #pragma unroll
       for (int q = 0; q < 4; q++) {
@@ -246,30 +297,36 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
     __syncthreads();
   }
   const float d_up = __uint_as_float((uint32_t)(127 + 133 - S) << 23);   // 2^(133-S)
-  const uint32_t x_base = smem_u32(smem + Smem::x);
-  const uint32_t zero_base = smem_u32(smem + Smem::zero(K));
   const bool live = (g >> 1) == t;
-  float* red = reinterpret_cast<float*>(smem + Smem::red(K));
+  const uint32_t x_lane_base = live ? smem_u32(smem + L.x) + g * 64 : smem_u32(smem + L.zero(K));
+  const uint32_t x_sb_stride = live ? 512u : 0u, x_step = live ? 16u : 0u;
+  const uint32_t xs_lane_base = smem_u32(xs) + 8 * t;
+  const LaneScale lc(t);
+  float* red = reinterpret_cast<float*>(smem + L.red(K));
 
-  float out0 = 0.f, out1 = 0.f;   // rows g and g+8 of this warp's tile, this lane's share
-  int flush_parity = 0;
-  for (int it = 0; it < n_units; ++it) {
-    // next unit's position and loads (one tile ahead)
-    int rg_n = rg, c_n = c + 1;
-    if (c_n == C) { c_n = 0; ++rg_n; }
-    if (it + 1 < n_units) {
-      const uint8_t *p0, *p1;
-      tile_ptrs(rg_n, c_n, p0, p1);
-      load_tile(nxt, p0, p1, t);
+  // ---- multiply side: walk my units row group by row group ----
+  int rg = rg_begin, c = c_begin, done = 0, slot = 0, flush_parity = 0;
+  while (done < n_units) {
+    const int c_first = c;
+    const int c_stop = min(C, c + (n_units - done));     // chunks [c, c_stop) of row group rg are mine
+    float out0 = 0.f, out1 = 0.f;                        // rows g and g+8 of this warp's tile, this lane's share
+    int sbg = c * kSbPerUnit + kSbPerWarp * j;
+    uint32_t xa = x_lane_base + (uint32_t)sbg * x_sb_stride;
+    uint32_t xsa = xs_lane_base + (uint32_t)sbg * 32u;
+    for (; c < c_stop; ++c) {
+      issue_next();                                      // keeps DEPTH - 1 steps in flight
+      cp_async_wait<DEPTH - 1>();                        // the oldest one has landed
+      __syncwarp();
+      const uint32_t tile = my_ring + slot * kSlotBytes;
+      if (sbg < SB) compute_tile(tile, g, t, lc, xa, x_step, xsa, out0, out1);
+      if (sbg + 1 < SB) compute_tile(tile + kBlockBytes, g, t, lc, xa + x_sb_stride, x_step, xsa + 32u, out0, out1);
+      __syncwarp();   // every lane is done with the slot before a later copy overwrites it
+      if (++slot == DEPTH) slot = 0;
+      sbg += kSbPerUnit;
+      xa += kSbPerUnit * x_sb_stride;
+      xsa += kSbPerUnit * 32u;
     }
-    const int sbg = c * kSbPerUnit + j;
-    if (sbg < SB) compute_tile(cur, sbg, g, t, live, x_base, zero_base, xs, d_up, out0, out1);
-    cur = nxt;
-
-    const bool last_of_rg = (c == C - 1) || (it + 1 == n_units);
-    const int rg_now = rg;
-    rg = rg_n; c = c_n;
-    if (!last_of_rg) continue;
+    done += c_stop - c_first;
 
     // ---- flush the row group: fold lanes, fold the warps that shared a row tile, publish ----
     float v0 = out0, v1 = out1;
@@ -277,58 +334,79 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
     v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 1); v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 2);
     float* redbuf = red + flush_parity * (kWarps * 16);
     if (t == 0) {
-      redbuf[warp * 16 + g] = v0;
-      redbuf[warp * 16 + g + 8] = v1;
+      redbuf[warp * 16 + g] = v0 * d_up;      // undo the power-of-two scaling of the activations
+      redbuf[warp * 16 + g + 8] = v1 * d_up;
     }
-    out0 = out1 = 0.f;
     flush_parity ^= 1;
     __syncthreads();
     if (warp == 0) {
-      const int tile = lane >> 4, r = lane & 15;
-      float v = 0.f;
+      const bool complete = (c_first == 0) && (c_stop == C);
+      const int64_t rg_first_unit = (int64_t)rg * C, rg_last_unit = rg_first_unit + C - 1;
+      float v[2];
 #pragma unroll
-      for (int jj = 0; jj < 8; jj++) v += redbuf[(tile * 8 + jj) * 16 + r];
-      const int row = rg_now * kRowsPerUnit + lane;
-      const int64_t rg_first_unit = (int64_t)rg_now * C, rg_last_unit = rg_first_unit + C - 1;
-      const bool complete = (u_begin <= rg_first_unit) && (u_end > rg_last_unit);
+      for (int h = 0; h < 2; h++) {
+        const int r = lane + 32 * h;            // row within the unit
+        v[h] = 0.f;
+        if (r < kRowsPerUnit) {
+#pragma unroll
+          for (int jj = 0; jj < 8; jj++) v[h] += redbuf[((r >> 4) * 8 + jj) * 16 + (r & 15)];
+        }
+      }
       if (complete) {
-        if (row < N) store_out(y, y_dtype, row, v);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          const int r = lane + 32 * h, row = rg * kRowsPerUnit + r;
+          if (r < kRowsPerUnit && row < N) store_out(y, y_dtype, row, v[h]);
+        }
       } else {
-        const int slot = (rg_now == (int)(u_begin / C)) ? 0 : 1;
-        __stcg(&partials[((int64_t)b * 2 + slot) * kRowsPerUnit + lane], v);
+        const int slot_p = (rg == rg_begin) ? 0 : 1;
+        float* mine = partials + ((int64_t)b * 2 + slot_p) * 64;
+        __stcg(&mine[lane], v[0]);
+        __stcg(&mine[lane + 32], v[1]);
         __threadfence();
         __syncwarp();
         const int bf = owner_of(rg_first_unit, U, G), bl = owner_of(rg_last_unit, U, G);
         int old = 0;
-        if (lane == 0) old = atomicAdd(&counters[rg_now], 1);
+        if (lane == 0) old = atomicAdd(&counters[rg], 1);
         old = __shfl_sync(0xFFFFFFFFu, old, 0);
-        if (old == bl - bf) {   // last of the bl - bf + 1 contributors
+        if (old == bl - bf) {   // last of the bl - bf + 1 contributors: add the partials in CTA order
           __threadfence();
-          float sum = 0.f;
+          float s0 = 0.f, s1 = 0.f;
           for (int bb = bf; bb <= bl; bb++) {
-            const int sl = (rg_now == (int)((U * bb / G) / C)) ? 0 : 1;
-            sum += __ldcg(&partials[((int64_t)bb * 2 + sl) * kRowsPerUnit + lane]);
+            const int sl = (rg == (int)((U * bb / G) / C)) ? 0 : 1;
+            const float* theirs = partials + ((int64_t)bb * 2 + sl) * 64;
+            s0 += __ldcg(&theirs[lane]);
+            s1 += __ldcg(&theirs[lane + 32]);
           }
-          if (row < N) store_out(y, y_dtype, row, sum);
-          if (lane == 0) counters[rg_now] = 0;
+          const int row0 = rg * kRowsPerUnit + lane, row1 = row0 + 32;
+          if (row0 < N) store_out(y, y_dtype, row0, s0);
+          if (lane + 32 < kRowsPerUnit && row1 < N) store_out(y, y_dtype, row1, s1);
+          if (lane == 0) counters[rg] = 0;
         }
       }
     }
+    if (c == C) { c = 0; ++rg; }
   }
+  cp_async_wait<0>();
 }
 
 }  // namespace q4k
 
 bool gemv_q4k_applicable(int64_t N, int64_t K, int M, const void* w, const void* x) {
-  return M == 1 && K % 256 == 0 && K <= q4k::kMaxK && N >= 1 && N < (1ll << 31) - 64 &&
-         (uintptr_t)w % 16 == 0 && (uintptr_t)x % 16 == 0;
+  return M == 1 && K % 256 == 0 && q4k::Smem(2).total((int)K) <= q4k::kSmemLimit && N >= 1 &&
+         N < (1ll << 31) - 64 && N * (K / 256 * 144) < (1ll << 40) && (uintptr_t)w % 16 == 0 && (uintptr_t)x % 16 == 0;
 }
 
+// Scratch layout: [partial slots: kMaxSmCount CTAs x 2 x 64 floats][arrival counters: one int per
+// row group].  The partial area has a fixed size and comes first, so that the counters of every
+// call, whatever its shape, live in bytes that only ever hold counters (which each launch leaves
+// at zero); partial slots may hold stale floats, they are always written before they are read.
+static constexpr size_t kPartialBytes = (size_t)kMaxSmCount * 2 * 64 * sizeof(float);
+
 size_t gemv_q4k_workspace_bytes(int64_t N, int sm_count) {
+  (void)sm_count;
   const int64_t RG = (N + q4k::kRowsPerUnit - 1) / q4k::kRowsPerUnit;
-  size_t counters = ((size_t)RG * sizeof(int) + 255) / 256 * 256;
-  size_t partials = (size_t)sm_count * 2 * q4k::kRowsPerUnit * sizeof(float);
-  return counters + partials;
+  return kPartialBytes + ((size_t)RG * sizeof(int) + 255) / 256 * 256;
 }
 
 cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void* y, int y_dtype, void* ws,
@@ -340,20 +418,25 @@ cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
   const int SB = (int)(K / 256);
   const int64_t U = RG * ((SB + kSbPerUnit - 1) / kSbPerUnit);
   const int grid = (int)(U < sm_count ? U : sm_count);
-  const int smem = Smem::total((int)K);
+  int depth = 3;
+  while (depth > 2 && Smem(depth).total((int)K) > kSmemLimit) depth--;
+  const int smem = Smem(depth).total((int)K);
+  if (smem > kSmemLimit) return cudaErrorInvalidValue;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_q4k_m1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Smem::total(kMaxK));
+    cudaError_t e = cudaFuncSetAttribute(gemv_q4k_m1_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q4k_m1_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
-  int* counters = reinterpret_cast<int*>(ws);
-  float* partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + ((size_t)RG * sizeof(int) + 255) / 256 * 256);
-  gemv_q4k_m1_kernel<<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, (const __nv_bfloat16*)x, y, y_dtype,
-                                                  counters, partials);
+  float* partials = reinterpret_cast<float*>(ws);
+  int* counters = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ws) + kPartialBytes);
+  if (sm_count > kMaxSmCount) return cudaErrorInvalidValue;
+  const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+  if (depth == 3) gemv_q4k_m1_kernel<3><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
+  else gemv_q4k_m1_kernel<2><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
   return cudaPeekAtLastError();
 }
 

@@ -199,3 +199,13 @@ def test_q4k_batch1_kernel_is_deterministic_and_leaves_scratch_clean():
                 assert O.rel_l2(got, O.c_matmul(O.bf16_bits(x), w, QT.Q4_K)) <= 2e-5
             else:
                 assert np.array_equal(got.view(np.uint32), first[(n, k)].view(np.uint32))
+
+
+def test_q4k_scratch_is_reusable_across_shapes():
+    """One scratch buffer serves calls of any shape in any order: a small weight followed by a
+    large one (whose arrival counters sit where the small call's partial sums could have gone)."""
+    for n, k in [(96, 512), (33, 9 * 256), (4752, 4096), (20_000, 256), (96, 512), (8192, 2048), (4736, 4096)]:
+        w = synth.make_weight_bytes(n, k, QT.Q4_K, seed=3)
+        x = synth.make_x(1, k, seed=4)
+        ref = O.c_matmul(O.bf16_bits(x), w, QT.Q4_K)
+        assert O.rel_l2(run_fused(x, w, QT.Q4_K, torch.float32), ref) <= 2e-5, (n, k)
