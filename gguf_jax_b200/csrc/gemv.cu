@@ -62,6 +62,18 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
   return GGQ_OK;
 }
 
+extern "C" int32_t ggq_gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x_bf16, void* y,
+                                       int32_t y_dtype, void* stream) {
+  if (y_dtype != GGQ_F32 && y_dtype != GGQ_BF16 && y_dtype != GGQ_F16)
+    return fail(GGQ_BAD_DTYPE, "ggq_gemv_q4k_static: y_dtype %d", y_dtype);
+  if (!w || !x_bf16 || !y) return fail(GGQ_MISALIGNED, "ggq_gemv_q4k_static: null pointer");
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int sms = sm_count_of(dev);
+  if (sms <= 0 || sms > kMaxSmCount) return fail(GGQ_LAUNCH_FAILED, "ggq_gemv_q4k_static: no usable CUDA device");
+  return gemv_q4k_static(w, N, K, x_bf16, y, y_dtype, sms, (cudaStream_t)stream);
+}
+
 extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
                             int32_t M, void* y, int32_t y_dtype, void* workspace, size_t workspace_bytes,
                             void* stream) {

@@ -22,6 +22,10 @@ size_t gemv_q4k_workspace_bytes(int64_t N, int sm_count);
 cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void* y, int y_dtype, void* ws,
                      size_t ws_bytes, int sm_count, int* status, cudaStream_t st);
 
+// Same kernel with the scratch in a file-scope device array (no caller buffer); returns a ggq_status.
+int32_t gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x, void* y, int32_t y_dtype,
+                        int sm_count, cudaStream_t st);
+
 // Upper bound on the SM count used when sizing scratch (the kernels use the real count).
 constexpr int kMaxSmCount = 256;
 

@@ -440,4 +440,60 @@ cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
   return cudaPeekAtLastError();
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// ggq_gemv_q4k_static: the same batch-1 Q4_K kernel for callers that cannot hand over scratch.
+//
+// Some hosts of this library are not allowed to allocate device memory around a call: a
+// custom-call handler whose framework owns every buffer and passes only operands and results,
+// code running between cudaStreamBeginCapture and EndCapture (where cudaMalloc is an error), a
+// serving loop with a fixed memory plan.  For them the partial-sum slots and arrival counters
+// live in the file-scope device array below instead of a caller buffer.  Every GPU that loads
+// the library carries these 192 KB until the process exits.
+//
+// In host code the array's name is only a host-side handle; the device address is obtained per
+// device with cudaGetSymbolAddress (with that device current) the first time the entry point
+// runs there, which is why that first call should be made outside any stream capture.
+// All calls on a device share the one array: calls whose kernels may overlap on the GPU
+// (different streams without an ordering between them) would mix their partial sums and must be
+// serialised by the caller.  The counters are cleared on the stream before every launch, so a
+// call never depends on what the previous one left behind.
+namespace q4k {
+constexpr int64_t kStaticMaxRows = 524288;                                      // output rows it can take
+static_assert(kRowsPerUnit >= 32, "the built-in scratch holds one counter per 32 rows");
+constexpr size_t kStaticCounterBytes = (size_t)(kStaticMaxRows / 32) * sizeof(int);
+constexpr size_t kStaticBytes = kPartialBytes + kStaticCounterBytes;             // 128 KB + 64 KB
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticBytes];
+}  // namespace q4k
+
+int32_t gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x, void* y, int32_t y_dtype,
+                        int sm_count, cudaStream_t st) {
+  using namespace q4k;
+  if (N < 1 || N > kStaticMaxRows)
+    return fail(GGQ_BAD_SHAPE, "ggq_gemv_q4k_static: N=%lld outside 1..%lld (the built-in scratch holds one "
+                "arrival counter per %d rows)", (long long)N, (long long)kStaticMaxRows, kRowsPerUnit);
+  if (!gemv_q4k_applicable(N, K, 1, w, x))
+    return fail(GGQ_BAD_SHAPE, "ggq_gemv_q4k_static: needs K a multiple of 256 with K <= %d and 16-byte aligned "
+                "w and x (got K=%lld)", (kSmemLimit - Smem(2).total(0)) / 2 / 256 * 256, (long long)K);
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess || dev < 0 || dev >= 64) return fail(GGQ_LAUNCH_FAILED, "ggq_gemv_q4k_static: no current device");
+  static uint8_t* dev_ptr[64] = {};
+  if (!dev_ptr[dev]) {
+    // once per device, with that device current: translate the symbol into a device address
+    uint8_t* p = nullptr;
+    err = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+    if (err != cudaSuccess || !p)
+      return fail(GGQ_LAUNCH_FAILED, "ggq_gemv_q4k_static: cudaGetSymbolAddress: %s", cudaGetErrorString(err));
+    dev_ptr[dev] = p;
+  }
+  uint8_t* scratch = dev_ptr[dev];
+  const int64_t RG = (N + kRowsPerUnit - 1) / kRowsPerUnit;
+  err = cudaMemsetAsync(scratch + kPartialBytes, 0, (size_t)RG * sizeof(int), st);   // counters start at zero
+  if (err == cudaSuccess)
+    err = gemv_q4k((const uint8_t*)w, N, K, x, y, y_dtype, scratch, kStaticBytes, sm_count, nullptr, st);
+  if (err != cudaSuccess) return fail(GGQ_LAUNCH_FAILED, "ggq_gemv_q4k_static: %s", cudaGetErrorString(err));
+  return GGQ_OK;
+}
+
 }  // namespace ggq

@@ -107,6 +107,22 @@ int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, const void*
                  int32_t M, void* y, int32_t y_dtype, void* workspace,
                  size_t workspace_bytes, void* stream);
 
+/* Batch-1 Q4_K multiply that needs no scratch from the caller and allocates nothing.
+ * No counterpart in the reference.  It exists for hosts that cannot allocate device memory
+ * around a call: a custom-call handler whose framework owns every buffer, code between
+ * cudaStreamBeginCapture and cudaStreamEndCapture (cudaMalloc is an error there), a serving
+ * loop with a fixed memory plan.  The scratch of ggq_gemv lives in a 192 KB device array
+ * built into the library (held by every GPU that loads it until the process exits), which
+ * bounds the weight to N <= 524288 rows; K as for the Q4_K path of ggq_gemv (multiple of 256,
+ * activations resident in shared memory), w and x 16-byte aligned, M = 1.  Larger N or an
+ * unsupported K returns GGQ_BAD_SHAPE with the limit in ggq_last_error().
+ * The first call on a device looks up the array's device address; make that first call
+ * outside any stream capture.  All calls on one device share the array: calls whose kernels
+ * could overlap on the GPU (unordered streams) must be serialised by the caller.  The result
+ * is identical to ggq_gemv on the same inputs. */
+int32_t ggq_gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x_bf16, void* y,
+                            int32_t y_dtype, void* stream);
+
 /* Reads and clears the device-side status word of `device` (0 = no bounded wait ran
  * out since the last read).  Synchronises the device.  No reference counterpart: the
  * reference has no device-side waits. */
