@@ -222,7 +222,9 @@ def run_ours(args) -> None:
         torch.cuda.synchronize()
         print(f"profile run: {args.warmup + args.steps} eager launches done", file=sys.stderr)
         if world > 1:
-            dist.destroy_process_group()
+            dist.barrier()
+            sys.stderr.flush()
+            os._exit(0)
         return
 
     stream = torch.cuda.Stream(dev)
@@ -349,8 +351,15 @@ def run_ours(args) -> None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line))
     if world > 1:
+        # Tear down without destroy_process_group(): with NCCL kernels captured in a CUDA graph it
+        # has been seen to block at exit.  Everything is flushed and every rank has passed the
+        # barrier, so a plain process exit is safe.
+        del graph
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main() -> None:
