@@ -5,6 +5,8 @@ using namespace ggq;
 
 namespace {
 constexpr int kGemvMaxBatch = 16;
+// Above this batch the dequantize-then-GEMM route (decode kernel + library bf16 GEMM) wins.
+constexpr int kGemmMaxBatch = 256;
 }
 
 extern "C" int32_t ggq_gemv_max_batch(void) { return kGemvMaxBatch; }
@@ -12,7 +14,7 @@ extern "C" int32_t ggq_gemv_max_batch(void) { return kGemvMaxBatch; }
 extern "C" int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K) {
   const TypeInfo* ti = type_info(qtype);
   if (!ti || !ti->fused || N <= 0 || K <= 0 || K % ti->block_elems) return 0;
-  return kGemvMaxBatch;
+  return gemm_applicable(ti, N, K, kGemmMaxBatch) ? kGemmMaxBatch : kGemvMaxBatch;
 }
 
 static int sm_count_of(int dev) {
@@ -77,7 +79,27 @@ extern "C" int32_t ggq_gemv_q4k_static(const void* w, int64_t N, int64_t K, cons
 extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
                             int32_t M, void* y, int32_t y_dtype, void* workspace, size_t workspace_bytes,
                             void* stream) {
-  (void)w; (void)N; (void)K; (void)x_bf16; (void)M; (void)y; (void)y_dtype;
-  (void)workspace; (void)workspace_bytes; (void)stream;
-  return fail(GGQ_UNSUPPORTED, "ggq_gemm: no tensor-core kernel for qtype %d yet", qtype);
+  (void)workspace; (void)workspace_bytes;
+  const TypeInfo* ti = type_info(qtype);
+  if (!ti) return fail(GGQ_BAD_QTYPE, "ggq_gemm: qtype %d is not decodable", qtype);
+  if (!ti->fused) return fail(GGQ_UNSUPPORTED, "ggq_gemm: no fused kernel for qtype %d", qtype);
+  if (N <= 0 || K <= 0 || K % ti->block_elems || M < 1)
+    return fail(GGQ_BAD_SHAPE, "ggq_gemm: N=%lld K=%lld M=%d (K must be a positive multiple of %d)",
+                (long long)N, (long long)K, M, ti->block_elems);
+  if (!gemm_applicable(ti, N, K, M))
+    return fail(GGQ_UNSUPPORTED, "ggq_gemm: shape N=%lld K=%lld M=%d is outside the tensor-core kernel's range "
+                "(K must be a multiple of 32)", (long long)N, (long long)K, M);
+  if (y_dtype != GGQ_F32 && y_dtype != GGQ_BF16 && y_dtype != GGQ_F16)
+    return fail(GGQ_BAD_DTYPE, "ggq_gemm: y_dtype %d", y_dtype);
+  if (!w || !x_bf16 || !y) return fail(GGQ_MISALIGNED, "ggq_gemm: null pointer");
+  if ((uintptr_t)x_bf16 % 16) return fail(GGQ_MISALIGNED, "ggq_gemm: x must be 16-byte aligned");
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const uint8_t* tab = device_tables(dev);
+  if (ti->needs_tables && !tab)
+    return fail(GGQ_NO_TABLES, "ggq_gemm: call ggq_set_tables(%d, ...) before using qtype %d", dev, qtype);
+  cudaError_t err = gemm_tf32(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, device_status_word(dev),
+                              (cudaStream_t)stream);
+  if (err != cudaSuccess) return fail(GGQ_LAUNCH_FAILED, "ggq_gemm: %s", cudaGetErrorString(err));
+  return GGQ_OK;
 }

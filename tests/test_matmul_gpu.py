@@ -209,3 +209,52 @@ def test_q4k_scratch_is_reusable_across_shapes():
         x = synth.make_x(1, k, seed=4)
         ref = O.c_matmul(O.bf16_bits(x), w, QT.Q4_K)
         assert O.rel_l2(run_fused(x, w, QT.Q4_K, torch.float32), ref) <= 2e-5, (n, k)
+
+
+# ---- the tcgen05 / TMEM kernel for larger batches (tf32 operands, float32 accumulation) ----
+
+GEMM_TYPES = [QT.Q4_K, QT.Q5_K, QT.Q6_K, QT.IQ4_XS, QT.Q8_0, QT.IQ2_XS, QT.Q2_K]
+
+
+@pytest.mark.parametrize("qtype", GEMM_TYPES, ids=lambda t: t.name)
+@pytest.mark.parametrize("m", [17, 32, 100, 128, 200, 256, 300, 512])
+def test_tensor_core_gemm_matches_oracle(qtype, m):
+    n, k = 200, 11 * 256           # one full and one ragged 128-row tile, 88 K blocks
+    w = synth.make_weight_bytes(n, k, qtype, seed=m)
+    x = synth.make_x(m, k, seed=m)
+    ref = O.c_matmul(O.bf16_bits(x), w, qtype)
+    got32 = run_fused(x, w, qtype, torch.float32)
+    # tf32 weights (11 significant bits, rounded to nearest): about 3e-4 relative L2
+    assert O.rel_l2(got32, ref) <= 1e-3, O.rel_l2(got32, ref)
+    check_close(run_fused(x, w, qtype), ref)
+
+
+def test_tensor_core_gemm_large_tile_counts():
+    for n, k, m in [(1024, 512, 64), (4096, 4096, 32), (130, 256, 20)]:
+        w = synth.make_weight_bytes(n, k, QT.Q4_K, seed=n)
+        x = synth.make_x(m, k, seed=n)
+        ref = O.c_matmul(O.bf16_bits(x), w, QT.Q4_K)
+        check_close(run_fused(x, w, QT.Q4_K), ref)
+
+
+def test_tensor_core_gemm_one_hot_columns():
+    """x = e_k returns the weight column: exact up to the tf32 rounding of the weight, i.e. the
+    bf16 result is the bf16 rounding of the float32 weight or its neighbour."""
+    n, k = 130, 512
+    w = synth.make_weight_bytes(n, k, QT.Q4_K, seed=2)
+    W = O.ref_dequantize(w, QT.Q4_K)
+    cols = list(range(0, 512, 16))
+    x = np.zeros((len(cols), k), dtype=np.float32)
+    x[np.arange(len(cols)), cols] = 1.0
+    got = run_fused(x, w, QT.Q4_K, torch.float32)
+    want = W[:, cols].T
+    np.testing.assert_allclose(got, want, rtol=2.0 ** -11, atol=0)
+
+
+def test_router_uses_the_tensor_core_kernel_between_the_caps():
+    w = synth.make_weight(256, 512, QT.Q4_K, seed=5)
+    cap = gj.fused_batch_limit(w)
+    assert cap > kernels.gemv_max_batch()
+    x = to_x(synth.make_x(cap, 512, seed=5))
+    ref = O.c_matmul(O.bf16_bits(x.float().cpu().numpy()), w.data.cpu().numpy(), QT.Q4_K)
+    check_close(gj.matmul(x, w).float().cpu().numpy(), ref)
