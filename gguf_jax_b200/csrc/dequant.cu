@@ -110,6 +110,8 @@ extern "C" int32_t ggq_dequant(int32_t qtype, const void* blocks, int64_t n_bloc
   if (n_blocks == 0) return GGQ_OK;
   if (!blocks || !out) return fail(GGQ_MISALIGNED, "ggq_dequant: null pointer");
   if ((uintptr_t)out % 16) return fail(GGQ_MISALIGNED, "ggq_dequant: out must be 16-byte aligned");
+  if ((uintptr_t)blocks % block_alignment(ti))
+    return fail(GGQ_MISALIGNED, "ggq_dequant: blocks must be %d-byte aligned for qtype %d", block_alignment(ti), qtype);
   int dev = 0;
   cudaGetDevice(&dev);
   const uint8_t* tab = device_tables(dev);

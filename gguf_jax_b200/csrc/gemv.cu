@@ -5,6 +5,8 @@ using namespace ggq;
 
 namespace {
 constexpr int kGemvMaxBatch = 16;
+// From this batch on the tensor-core small-batch kernel beats the per-element FMA kernel.
+constexpr int kMmaMinBatch = 2;
 // Above this batch the dequantize-then-GEMM route (decode kernel + library bf16 GEMM) wins.
 constexpr int kGemmMaxBatch = 256;
 }
@@ -45,6 +47,8 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
     return fail(GGQ_BAD_DTYPE, "ggq_gemv: y_dtype %d", y_dtype);
   if (!w || !x_bf16 || !y) return fail(GGQ_MISALIGNED, "ggq_gemv: null pointer");
   if ((uintptr_t)x_bf16 % 16) return fail(GGQ_MISALIGNED, "ggq_gemv: x must be 16-byte aligned");
+  if ((uintptr_t)w % block_alignment(ti))
+    return fail(GGQ_MISALIGNED, "ggq_gemv: w must be %d-byte aligned for qtype %d", block_alignment(ti), qtype);
   int dev = 0;
   cudaGetDevice(&dev);
   const uint8_t* tab = device_tables(dev);
@@ -57,6 +61,8 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
       sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount) {
     err = gemv_q4k((const uint8_t*)w, N, K, x_bf16, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev),
                    device_status_word(dev), st);
+  } else if (gemv_mma_applicable(ti, N, K, M) && M >= kMmaMinBatch) {
+    err = gemv_mma(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, st);
   } else {
     err = gemv_generic(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, st);
   }
@@ -93,6 +99,8 @@ extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, 
     return fail(GGQ_BAD_DTYPE, "ggq_gemm: y_dtype %d", y_dtype);
   if (!w || !x_bf16 || !y) return fail(GGQ_MISALIGNED, "ggq_gemm: null pointer");
   if ((uintptr_t)x_bf16 % 16) return fail(GGQ_MISALIGNED, "ggq_gemm: x must be 16-byte aligned");
+  if ((uintptr_t)w % block_alignment(ti))
+    return fail(GGQ_MISALIGNED, "ggq_gemm: w must be %d-byte aligned for qtype %d", block_alignment(ti), qtype);
   int dev = 0;
   cudaGetDevice(&dev);
   const uint8_t* tab = device_tables(dev);

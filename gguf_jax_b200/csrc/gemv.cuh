@@ -26,6 +26,12 @@ cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
 int32_t gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x, void* y, int32_t y_dtype,
                         int sm_count, cudaStream_t st);
 
+// Any block qtype, M <= 16, K a multiple of 32: tensor-core kernel with exact three-way bf16 split
+// of the decoded weights (gemv_mma.cu).
+bool gemv_mma_applicable(const TypeInfo* ti, int64_t N, int64_t K, int M);
+cudaError_t gemv_mma(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y,
+                     int y_dtype, const uint8_t* tab, cudaStream_t st);
+
 // Larger batches: tcgen05 / TMEM tensor-core kernel with tf32 operands (gemm_tcgen05.cu).
 bool gemm_applicable(const TypeInfo* ti, int64_t N, int64_t K, int M);
 cudaError_t gemm_tf32(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y,

@@ -37,6 +37,14 @@ struct TypeInfo { int qtype, block_elems, block_bytes; bool needs_tables; bool f
 // Returns nullptr for a qtype outside the 26 decodable ones.
 const TypeInfo* type_info(int qtype);
 
+// Alignment every block of a tensor has when the tensor starts 16-byte aligned: gcd(block bytes, 16).
+// The decoders load with this width, so quantized pointers handed to the ABI must honour it.
+inline int block_alignment(const TypeInfo* ti) {
+  int a = 16;
+  while (ti->block_bytes % a) a >>= 1;
+  return a;
+}
+
 // Per-device immutable state owned by the library (capi.cu).
 const uint8_t* device_tables(int device);    // nullptr until ggq_set_tables(device, ...)
 int* device_status_word(int device);         // allocated lazily with the tables

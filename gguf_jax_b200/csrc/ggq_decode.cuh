@@ -22,6 +22,27 @@ __device__ __forceinline__ uint32_t ld16(const uint8_t* p) { return ldb(p) | (ld
 __device__ __forceinline__ uint32_t ld32(const uint8_t* p) {
   return ldb(p) | (ldb(p + 1) << 8) | (ldb(p + 2) << 16) | (ldb(p + 3) << 24);
 }
+// Eight consecutive block bytes as two little-endian words, with loads as wide as the block's
+// alignment allows.  ALIGN is the guaranteed alignment of p: a tensor starts 16-byte aligned and
+// every block starts a multiple of its size further on, so ALIGN = gcd(block bytes, 16) combined
+// with the (even) offset inside the block.
+template <int ALIGN>
+__device__ __forceinline__ uint2 ld8(const uint8_t* p) {
+  if constexpr (ALIGN >= 8) {
+    return __ldg(reinterpret_cast<const uint2*>(p));
+  } else if constexpr (ALIGN >= 4) {
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(p);
+    return make_uint2(__ldg(q), __ldg(q + 1));
+  } else if constexpr (ALIGN >= 2) {
+    const unsigned short* q = reinterpret_cast<const unsigned short*>(p);
+    return make_uint2((uint32_t)__ldg(q) | ((uint32_t)__ldg(q + 1) << 16),
+                      (uint32_t)__ldg(q + 2) | ((uint32_t)__ldg(q + 3) << 16));
+  } else {
+    return make_uint2(ld32(p), ld32(p + 4));
+  }
+}
+__device__ __forceinline__ uint32_t byte_of(const uint2& v, int i) { return ((i < 4 ? v.x : v.y) >> (8 * (i & 3))) & 0xFF; }
+
 // IEEE half bits -> float (exact; cvt.f32.f16 keeps subnormals).
 __device__ __forceinline__ float h2f(uint32_t bits) {
   return __half2float(__ushort_as_half((unsigned short)bits));
@@ -108,9 +129,10 @@ template <> struct Dec<QT_Q5_1> {
 };
 template <> struct Dec<QT_Q8_0> {
   __device__ static void run(const uint8_t* b, int g, const uint8_t*, float* o) {
-    float d = h2f(ld16(b));
+    float d = h2f(__ldg(reinterpret_cast<const unsigned short*>(b)));
+    const uint2 q = ld8<2>(b + 2 + 8 * g);
 #pragma unroll
-    for (int i = 0; i < 8; i++) o[i] = __fmul_rn(i2f((int8_t)ldb(b + 2 + 8 * g + i)), d);
+    for (int i = 0; i < 8; i++) o[i] = __fmul_rn(i2f((int8_t)byte_of(q, i)), d);
   }
 };
 template <> struct Dec<QT_IQ4_NL> {
@@ -185,45 +207,57 @@ template <> struct Dec<QT_Q3_K> {
     }
   }
 };
+// Q4_K / Q5_K blocks are 144 / 176 bytes: always 16-byte aligned, so the header is one
+// 128-bit load and the eight quant bytes one 64-bit load.
+__device__ __forceinline__ void scale_min_k4_words(const uint4& h, int k, int& sc, int& mn) {
+  // h = (d|dmin, s0-3, s4-7, s8-11); same unpack as scale_min_k4
+  const int sh = 8 * (k & 3);
+  const uint32_t a = (h.y >> sh) & 0xFF, m = (h.z >> sh) & 0xFF, md = (h.w >> sh) & 0xFF;
+  if (k < 4) { sc = a & 63; mn = m & 63; }
+  else { sc = (md & 15) | ((a >> 6) << 4); mn = (md >> 4) | ((m >> 6) << 4); }
+}
 template <> struct Dec<QT_Q4_K> {
   __device__ static void run(const uint8_t* b, int g, const uint8_t*, float* o) {
-    float d = h2f(ld16(b)), dmin = h2f(ld16(b + 2));
+    const uint4 h = __ldg(reinterpret_cast<const uint4*>(b));
+    const float d = h2f(h.x & 0xFFFF), dmin = h2f(h.x >> 16);
     int k = g >> 2, sc, mn;
-    scale_min_k4(b + 4, k, sc, mn);
+    scale_min_k4_words(h, k, sc, mn);
     float dl = __fmul_rn(d, i2f(sc)), dm = __fmul_rn(dmin, i2f(mn));
-    const uint8_t* qs = b + 16 + 32 * (k >> 1) + 8 * (g & 3);
+    const uint2 q = ld8<8>(b + 16 + 32 * (k >> 1) + 8 * (g & 3));
     int sh = 4 * (k & 1);
 #pragma unroll
-    for (int i = 0; i < 8; i++) o[i] = __fsub_rn(__fmul_rn(dl, i2f((ldb(qs + i) >> sh) & 15)), dm);
+    for (int i = 0; i < 8; i++) o[i] = __fsub_rn(__fmul_rn(dl, i2f((byte_of(q, i) >> sh) & 15)), dm);
   }
 };
 template <> struct Dec<QT_Q5_K> {
   __device__ static void run(const uint8_t* b, int g, const uint8_t*, float* o) {
-    float d = h2f(ld16(b)), dmin = h2f(ld16(b + 2));
+    const uint4 h = __ldg(reinterpret_cast<const uint4*>(b));
+    const float d = h2f(h.x & 0xFFFF), dmin = h2f(h.x >> 16);
     int k = g >> 2, sc, mn;
-    scale_min_k4(b + 4, k, sc, mn);
+    scale_min_k4_words(h, k, sc, mn);
     float dl = __fmul_rn(d, i2f(sc)), dm = __fmul_rn(dmin, i2f(mn));
-    const uint8_t* qh = b + 16 + 8 * (g & 3);
-    const uint8_t* qs = b + 48 + 32 * (k >> 1) + 8 * (g & 3);
+    const uint2 qh = ld8<8>(b + 16 + 8 * (g & 3));
+    const uint2 qs = ld8<8>(b + 48 + 32 * (k >> 1) + 8 * (g & 3));
     int sh = 4 * (k & 1);
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      int q = ((ldb(qs + i) >> sh) & 15) | (((ldb(qh + i) >> k) & 1) << 4);
+      int q = ((byte_of(qs, i) >> sh) & 15) | (((byte_of(qh, i) >> k) & 1) << 4);
       o[i] = __fsub_rn(__fmul_rn(dl, i2f(q)), dm);
     }
   }
 };
+// Q6_K blocks are 210 bytes: 2-byte aligned, all offsets below are even.
 template <> struct Dec<QT_Q6_K> {
   __device__ static void run(const uint8_t* b, int g, const uint8_t*, float* o) {
-    float d = h2f(ld16(b + 208));
+    float d = h2f(__ldg(reinterpret_cast<const unsigned short*>(b + 208)));
     float dl = __fmul_rn(d, i2f((int8_t)ldb(b + 192 + (g >> 1))));
     int c = g >> 2, t0 = 8 * (g & 3);
-    const uint8_t* ql = b + 64 * (c >> 2) + 32 * (c & 1) + t0;
-    const uint8_t* qh = b + 128 + 32 * (c >> 2) + t0;
+    const uint2 ql = ld8<2>(b + 64 * (c >> 2) + 32 * (c & 1) + t0);
+    const uint2 qh = ld8<2>(b + 128 + 32 * (c >> 2) + t0);
     int shl = 4 * ((c >> 1) & 1), shh = 2 * (c & 3);
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      int q = ((ldb(ql + i) >> shl) & 15) | (((ldb(qh + i) >> shh) & 3) << 4);
+      int q = ((byte_of(ql, i) >> shl) & 15) | (((byte_of(qh, i) >> shh) & 3) << 4);
       o[i] = __fmul_rn(dl, i2f(q - 32));
     }
   }
