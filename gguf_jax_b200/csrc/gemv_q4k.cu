@@ -55,11 +55,13 @@ constexpr int kRowTiles = 2;                   // 16-row tiles per unit
 constexpr int kWarps = 8 * kRowTiles;          // one warp per (row tile, superblock pair of the chunk)
 constexpr int kThreads = kWarps * 32;
 constexpr int kRowsPerUnit = 16 * kRowTiles;
-constexpr int kSbPerWarp = 2;                  // adjacent superblocks a warp multiplies per step (288 B per row)
+constexpr int kSbPerWarp = 2;                  // adjacent superblocks a warp multiplies per step
 constexpr int kSbPerUnit = 8 * kSbPerWarp;
 constexpr int kTileBytes = 16 * kBlockBytes;   // 2304
-constexpr int kSlotPitch = kSbPerWarp * kBlockBytes + 16;   // 304 = 48 (mod 128): conflict-free 128-bit reads
-constexpr int kSlotBytes = 16 * kSlotPitch;                // one warp's step: 16 rows x 288 B (+ 16 B pad)
+// Row pitch of a slot, chosen so that the 128-bit reads of a quarter-warp (two rows x four lanes)
+// fall into distinct banks: 144 = 16 (mod 128) for one superblock per step, 304 = 48 (mod 128) for two.
+constexpr int kSlotPitch = kSbPerWarp == 1 ? kBlockBytes : kSbPerWarp * kBlockBytes + 16;
+constexpr int kSlotBytes = 16 * kSlotPitch;                // one warp's step: 16 rows of kSbPerWarp superblocks
 constexpr int kSmemLimit = 232448;             // 227 KB opt-in limit per CTA
 
 struct Smem {
@@ -74,10 +76,9 @@ struct Smem {
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// A plain (schedulable) 128-bit shared-memory load from a shared-window address.
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
+  return *reinterpret_cast<const uint4*>(__cvta_shared_to_generic(addr));
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const uint8_t* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -85,20 +86,14 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const uint8_t* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// Not volatile: the instruction is a pure function of its operands, and leaving the compiler free
+// to interleave independent accumulation chains and the next tile's loads is worth a lot here.
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// x >> S computed as the high word of x * 2^(32-S): an integer multiply-add (FMA pipe) instead
-// of a shift (ALU pipe, half rate and the busiest pipe of this kernel).
-template <int S>
-__device__ __forceinline__ uint32_t shr_fma(uint32_t x) {
-  uint32_t r;
-  asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(1u << (32 - S)));
-  return r;
 }
 // byte `SEL` (0..3) of x as a float, exact: bits 0x4B0000vv are 2^23 + v.
 template <int SEL>
@@ -150,8 +145,7 @@ __device__ __forceinline__ void compute_tile(uint32_t tile, int g, int t, const 
   // A lane feeds column g of the B operand; that column is live only in the k-slots of lane
   // group g/2, so every other lane reads the zero page (base = zero page, strides = 0).
   const uint4 x0 = lds128(xa), x1 = lds128(xa + x_step), x2 = lds128(xa + 2 * x_step), x3 = lds128(xa + 3 * x_step);
-  float2 sx;   // X[2t], X[2t+1], already scaled like the accumulators
-  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(sx.x), "=f"(sx.y) : "r"(xsa));
+  const float2 sx = *reinterpret_cast<const float2*>(__cvta_shared_to_generic(xsa));   // X[2t], X[2t+1], scaled
 
   // Two accumulator tiles: the low-nibble pass and the high-nibble pass both multiply by this
   // lane's activations; only column 2t of the first and 2t+1 of the second are kept.
@@ -166,7 +160,7 @@ __device__ __forceinline__ void compute_tile(uint32_t tile, int g, int t, const 
     // nibbles) and 2t+1 (high nibbles).  Bytes (0,2) fill k-slots 2t,2t+1; bytes (1,3) fill
     // k-slots 2t+8,2t+9, matching the pair-permuted activations.
     const uint32_t a = w0[i], b = w1[i];
-    const uint32_t as = shr_fma<8>(a), bs = shr_fma<8>(b);
+    const uint32_t as = a >> 8, bs = b >> 8;   // (an integer-multiply shift on the FMA pipe measured 4 us slower)
     mma16816(lo, a & 0x000F000Fu, b & 0x000F000Fu, as & 0x000F000Fu, bs & 0x000F000Fu, xr[2 * i], xr[2 * i + 1]);
     mma16816(hi, a & 0x00F000F0u, b & 0x00F000F0u, as & 0x00F000F0u, bs & 0x00F000F0u, xr[2 * i], xr[2 * i + 1]);
   }
@@ -208,9 +202,13 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
   // The last row group of a weight whose N is not a multiple of 32 takes a slower path that
   // clamps every row to N - 1 (copied, multiplied, never stored); a missing second superblock
   // (odd K/256) is never multiplied, its 144 bytes are simply not copied.
-  const int hl = lane >> 4, kl = lane & 15;
-  const int32_t src_a = hl * row_bytes + 16 * kl, src_b = (lane >> 1) * row_bytes + 256 + 16 * (lane & 1);
-  const uint32_t dst_a = hl * kSlotPitch + 16 * kl, dst_b = (lane >> 1) * kSlotPitch + 256 + 16 * (lane & 1);
+  // two-superblock steps: 8 instructions copy pieces 0..15 of two rows each, a ninth pieces 16..17
+  // of all rows; one-superblock steps: 6 instructions copy the 9 pieces of three rows each.
+  const int hl = lane >> 4, kl = lane & 15, r3 = lane / 9, k9 = lane - 9 * r3;
+  const int32_t src_a = kSbPerWarp == 2 ? hl * row_bytes + 16 * kl : r3 * row_bytes + 16 * k9;
+  const int32_t src_b = (lane >> 1) * row_bytes + 256 + 16 * (lane & 1);
+  const uint32_t dst_a = kSbPerWarp == 2 ? hl * kSlotPitch + 16 * kl : r3 * kSlotPitch + 16 * k9;
+  const uint32_t dst_b = (lane >> 1) * kSlotPitch + 256 + 16 * (lane & 1);
   const uint8_t* src = w;        // first source byte of the next step
   int rg_i = rg_begin, c_i = c_begin, issued = 0, slot_i = 0;
   auto seek_row_group = [&]() {
@@ -223,12 +221,20 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
       const int sb0 = c_i * kSbPerUnit + kSbPerWarp * j;
       const uint32_t dst = my_ring + slot_i * kSlotBytes;
       const int row0 = rg_i * kRowsPerUnit + 16 * rt;
-      if (sb0 + 1 < SB && row0 + 16 <= N) {
-        // common case: both superblocks and all sixteen rows exist
+      if (sb0 + kSbPerWarp <= SB && row0 + 16 <= N) {
+        // common case: every superblock of the step and all sixteen rows exist
         const uint8_t* pa = src + src_a;
+        if constexpr (kSbPerWarp == 2) {
 #pragma unroll
-        for (int i = 0; i < 8; i++) cp_async16(dst + dst_a + i * (2 * kSlotPitch), pa + (int64_t)i * (2 * row_bytes));
-        cp_async16(dst + dst_b, src + src_b);
+          for (int i = 0; i < 8; i++) cp_async16(dst + dst_a + i * (2 * kSlotPitch), pa + (int64_t)i * (2 * row_bytes));
+          cp_async16(dst + dst_b, src + src_b);
+        } else {
+          if (lane < 27) {
+#pragma unroll
+            for (int i = 0; i < 5; i++) cp_async16(dst + dst_a + i * (3 * kSlotPitch), pa + (int64_t)i * (3 * row_bytes));
+          }
+          if (lane < 9) cp_async16(dst + dst_a + 15 * kSlotPitch, pa + (int64_t)15 * row_bytes);
+        }
       } else if (sb0 < SB) {
         const int nsb = min(kSbPerWarp, SB - sb0);
         for (int p = lane; p < 16 * 9 * nsb; p += 32) {
@@ -319,7 +325,9 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
       __syncwarp();
       const uint32_t tile = my_ring + slot * kSlotBytes;
       if (sbg < SB) compute_tile(tile, g, t, lc, xa, x_step, xsa, out0, out1);
-      if (sbg + 1 < SB) compute_tile(tile + kBlockBytes, g, t, lc, xa + x_sb_stride, x_step, xsa + 32u, out0, out1);
+      if constexpr (kSbPerWarp == 2) {
+        if (sbg + 1 < SB) compute_tile(tile + kBlockBytes, g, t, lc, xa + x_sb_stride, x_step, xsa + 32u, out0, out1);
+      }
       __syncwarp();   // every lane is done with the slot before a later copy overwrites it
       if (++slot == DEPTH) slot = 0;
       sbg += kSbPerUnit;
@@ -418,7 +426,7 @@ cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
   const int SB = (int)(K / 256);
   const int64_t U = RG * ((SB + kSbPerUnit - 1) / kSbPerUnit);
   const int grid = (int)(U < sm_count ? U : sm_count);
-  int depth = 3;
+  int depth = 4;
   while (depth > 2 && Smem(depth).total((int)K) > kSmemLimit) depth--;
   const int smem = Smem(depth).total((int)K);
   if (smem > kSmemLimit) return cudaErrorInvalidValue;
@@ -426,7 +434,8 @@ cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_q4k_m1_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    cudaError_t e = cudaFuncSetAttribute(gemv_q4k_m1_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q4k_m1_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q4k_m1_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
@@ -435,7 +444,8 @@ cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
   int* counters = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ws) + kPartialBytes);
   if (sm_count > kMaxSmCount) return cudaErrorInvalidValue;
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
-  if (depth == 3) gemv_q4k_m1_kernel<3><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
+  if (depth == 4) gemv_q4k_m1_kernel<4><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
+  else if (depth == 3) gemv_q4k_m1_kernel<3><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
   else gemv_q4k_m1_kernel<2><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
   return cudaPeekAtLastError();
 }
