@@ -47,8 +47,8 @@ UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from
 # the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
-NCU_TRAFFIC_SOURCE = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 136_600_000
+NCU_TRAFFIC_SOURCE = "profiles/q4k_gemv_m1_8192x28672.md (dram__bytes_read.sum + dram__bytes_write.sum, ncu --set full, 1 GPU, full weight)"
 
 
 def algorithmic_bytes(n: int, k: int, m: int, out_itemsize: int = 2) -> int:
@@ -337,7 +337,8 @@ def run_ours(args) -> None:
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "peak_source": peak_src,
-                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "traffic_source": NCU_TRAFFIC_SOURCE,
+                "traffic": (NCU_TRAFFIC_BYTES_PER_LAUNCH * rows_local // N_ROWS) if NCU_TRAFFIC_BYTES_PER_LAUNCH else None,
+                "traffic_source": NCU_TRAFFIC_SOURCE,
                 "algorithmic_bytes_per_launch": launch_bytes, "launch_us": launch_ms * 1e3,
             },
             "clocks": clk,
