@@ -70,6 +70,44 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
   return GGQ_OK;
 }
 
+extern "C" int32_t ggq_gemv_sharded(int32_t qtype, const void* w, int64_t N_local, int64_t K, const void* x_bf16,
+                                    int32_t M, void* const* y_peers, uint32_t* const* flag_peers, int32_t world,
+                                    int32_t rank, int64_t n_total, int32_t y_dtype, int32_t wait_previous,
+                                    void* workspace, size_t workspace_bytes, void* stream) {
+  const TypeInfo* ti = type_info(qtype);
+  if (!ti) return fail(GGQ_BAD_QTYPE, "ggq_gemv_sharded: qtype %d is not decodable", qtype);
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+    return fail(GGQ_BAD_SHAPE, "ggq_gemv_sharded: rank %d of %d (at most %d ranks)", rank, world, kMaxPeers);
+  if (N_local <= 0 || K <= 0 || K % ti->block_elems || n_total < (int64_t)world * N_local)
+    return fail(GGQ_BAD_SHAPE, "ggq_gemv_sharded: N_local=%lld K=%lld n_total=%lld", (long long)N_local,
+                (long long)K, (long long)n_total);
+  if (y_dtype != GGQ_F32 && y_dtype != GGQ_BF16 && y_dtype != GGQ_F16)
+    return fail(GGQ_BAD_DTYPE, "ggq_gemv_sharded: y_dtype %d", y_dtype);
+  if (!w || !x_bf16 || !y_peers || !flag_peers) return fail(GGQ_MISALIGNED, "ggq_gemv_sharded: null pointer");
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(qtype == QT_Q4_K && gemv_q4k_applicable(N_local, K, M, w, x_bf16)))
+    return fail(GGQ_UNSUPPORTED, "ggq_gemv_sharded: only the Q4_K batch-1 kernel publishes to peers so far; "
+                "use ggq_gemv plus an all-gather for qtype %d, M=%d", qtype, M);
+  if (!workspace || workspace_bytes < gemv_q4k_workspace_bytes(N_local, kMaxSmCount) || (uintptr_t)workspace % 256)
+    return fail(GGQ_BAD_WORKSPACE, "ggq_gemv_sharded: workspace of %zu bytes needed", gemv_q4k_workspace_bytes(N_local, kMaxSmCount));
+  PeerPublish pp = {};
+  for (int p = 0; p < world; p++) {
+    if (!y_peers[p] || !flag_peers[p]) return fail(GGQ_MISALIGNED, "ggq_gemv_sharded: null peer pointer %d", p);
+    pp.y[p] = y_peers[p];
+    pp.flags[p] = flag_peers[p];
+  }
+  pp.world = world;
+  pp.rank = rank;
+  pp.n_total = n_total;
+  pp.row_offset = (int64_t)rank * N_local;
+  pp.wait_previous = wait_previous ? 1 : 0;
+  cudaError_t err = gemv_q4k((const uint8_t*)w, N_local, K, x_bf16, nullptr, y_dtype, workspace, workspace_bytes,
+                             sm_count_of(dev), device_status_word(dev), (cudaStream_t)stream, &pp);
+  if (err != cudaSuccess) return fail(GGQ_LAUNCH_FAILED, "ggq_gemv_sharded: %s", cudaGetErrorString(err));
+  return GGQ_OK;
+}
+
 extern "C" int32_t ggq_gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x_bf16, void* y,
                                        int32_t y_dtype, void* stream) {
   if (y_dtype != GGQ_F32 && y_dtype != GGQ_BF16 && y_dtype != GGQ_F16)

@@ -16,11 +16,35 @@ __device__ __forceinline__ void store_out(void* y, int y_dtype, int64_t idx, flo
 cudaError_t gemv_generic(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K, const void* x, int M,
                          void* y, int y_dtype, const uint8_t* tab, cudaStream_t st);
 
-// Q4_K, batch 1: TMA-staged tensor-core kernel (gemv_q4k.cu).
+// Row-sharded output over several GPUs of one node (one process per GPU).  Instead of writing
+// y into a local buffer and all-gathering it, a kernel can store its slice of the output rows
+// straight into every peer's copy of y (peer-mapped pointers over NVLink) and, when the whole
+// grid has finished, raise a per-rank sequence flag in every peer's flag array.  The consumer
+// side is the same structure seen from the other end: before a kernel reads activations that a
+// previous exchange produced, it waits (bounded) until every rank's flag has reached the
+// sequence number of that exchange.  Plain stores and loads only; no multicast of any kind.
+constexpr int kMaxPeers = 8;
+struct PeerPublish {
+  void* y[kMaxPeers];             // every rank's full (M, n_total) output buffer, index = rank
+  uint32_t* flags[kMaxPeers];     // every rank's flag array (uint32[world]), index = rank
+  int world;                      // 0: not sharded (write y locally, no flags)
+  int rank;
+  int64_t n_total;                // row stride of the full output
+  int64_t row_offset;             // first output row of this rank's slice
+  int wait_previous;              // 1: the activations come from the previous exchange, wait for it first
+  // Each flag array has world + 2 words: [0, world) are raised by the peers; word `world` is this
+  // rank's epoch (number of exchanges it has published), word world + 1 counts finished CTAs of
+  // the running launch.  All ranks issue the same sequence of sharded launches, so "the previous
+  // exchange" is the one whose number equals this rank's own epoch: no host-side sequence
+  // numbers, and a captured CUDA graph can be replayed.
+};
+
+// Q4_K, batch 1: cp.async-staged tensor-core kernel (gemv_q4k.cu).
 bool gemv_q4k_applicable(int64_t N, int64_t K, int M, const void* w, const void* x);
 size_t gemv_q4k_workspace_bytes(int64_t N, int sm_count);
 cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void* y, int y_dtype, void* ws,
-                     size_t ws_bytes, int sm_count, int* status, cudaStream_t st);
+                     size_t ws_bytes, int sm_count, int* status, cudaStream_t st,
+                     const PeerPublish* peers = nullptr);
 
 // Same kernel with the scratch in a file-scope device array (no caller buffer); returns a ggq_status.
 int32_t gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x, void* y, int32_t y_dtype,

@@ -176,7 +176,8 @@ __device__ __forceinline__ void compute_tile(uint32_t tile, int g, int t, const 
 template <int DEPTH>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat16* __restrict__ x,
-                   void* __restrict__ y, int y_dtype, int* __restrict__ counters, float* __restrict__ partials) {
+                   void* __restrict__ y, int y_dtype, int* __restrict__ counters, float* __restrict__ partials,
+                   const PeerPublish pp, int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int SB = K / 256;                        // superblocks per row
@@ -262,45 +263,85 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
     // memory as scaled, pair-permuted bf16: word 2i = (x[4i], x[4i+2]), word 2i+1 = (x[4i+1], x[4i+3]).
     if (tid < 16) reinterpret_cast<uint32_t*>(smem + L.zero(K))[tid] = 0;
     if (tid == 0) *xmax = 0;
+    if (pp.world > 0 && pp.wait_previous && tid < pp.world) {
+      // The activations were produced by the previous exchange, whose number is this rank's own
+      // epoch: wait until every rank has raised its flag here to that number.  Bounded; when it
+      // runs out the status word is raised and the launch carries on (its result is then
+      // meaningless, the host sees GGQ_TIMEOUT).
+      const uint32_t* mine = pp.flags[pp.rank];
+      const uint32_t target = mine[pp.world];
+      // poll for at most ~50 ms of wall time
+      bool ok = false;
+      uint64_t t0;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+      for (uint32_t i = 0; i < (1u << 26) && !ok; i++) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + tid) : "memory");
+        ok = (int32_t)(v - target) >= 0;
+        if (!ok && (i & 63) == 63) {
+          uint64_t t1;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+          if (t1 - t0 > 50000000ull) break;
+        }
+      }
+      if (!ok && status) atomicOr(status, STATUS_WAIT_EXPIRED);
+    }
     __syncthreads();
     const uint4* xg = reinterpret_cast<const uint4*>(x);
     uint4* xv = reinterpret_cast<uint4*>(smem + L.x);
-    uint32_t mx = 0;
-    for (int sblk = tid; sblk < K / 32; sblk += kThreads) {
-      float sum = 0.f;
+    // One pass: read x once, accumulate the sub-block sum and the largest magnitude, and store the
+    // activations scaled by 2^S_ (2^(S_-4) for odd sub-blocks) in pair-permuted order.
+    auto stage_x = [&](int S_) -> float {
+      const float up_even = __uint_as_float((uint32_t)(127 + S_) << 23);
+      const float up_odd = __uint_as_float((uint32_t)(127 + S_ - 4) << 23);
+      const float xs_scale = __uint_as_float((uint32_t)(127 + S_ - 133) << 23);   // sums follow the accumulators' scale
+      float amax = 0.f;   // largest sum of |x| over a sub-block: within a factor 32 of the largest |x|
+      // Every CTA needs all of x; start each one at a different place so that the CTAs do not read
+      // the same L2 lines in lockstep.
+      const int n_sub = K / 32;
+      const int rot = (int)(((int64_t)b * n_sub) / G) & ~1;      // even: keeps sub-block parity
+      for (int i = tid; i < n_sub; i += kThreads) {
+        int sblk = i + rot;
+        if (sblk >= n_sub) sblk -= n_sub;
+        const float up = (sblk & 1) ? up_odd : up_even;
+        uint4 v[4];
 #pragma unroll
-      for (int q = 0; q < 4; q++) {
-        const uint4 v = __ldg(xg + sblk * 4 + q);
-        sum += bf16lo(v.x); sum += bf16hi(v.x); sum += bf16lo(v.y); sum += bf16hi(v.y);
-        sum += bf16lo(v.z); sum += bf16hi(v.z); sum += bf16lo(v.w); sum += bf16hi(v.w);
-        mx = max(mx, max(max(v.x & 0x7FFFu, (v.x >> 16) & 0x7FFFu), max(v.y & 0x7FFFu, (v.y >> 16) & 0x7FFFu)));
-        mx = max(mx, max(max(v.z & 0x7FFFu, (v.z >> 16) & 0x7FFFu), max(v.w & 0x7FFFu, (v.w >> 16) & 0x7FFFu)));
-      }
-      xs[sblk] = sum;
-    }
-    atomicMax(xmax, (int)mx);
-    __syncthreads();
-    // biased exponent of the largest |x|; keep x * 2^S below 2^126 and 2^(133-S) a normal float
-    const int emax = min((*xmax >> 7) & 0xFF, 254);
-    S = max(8, min(64, 252 - emax));
-    const float up_even = __uint_as_float((uint32_t)(127 + S) << 23);
-    const float up_odd = __uint_as_float((uint32_t)(127 + S - 4) << 23);
-    const float xs_scale = __uint_as_float((uint32_t)(127 + S - 133) << 23);   // sums follow the accumulators' scale
-    for (int sblk = tid; sblk < K / 32; sblk += kThreads) {
-      xs[sblk] *= xs_scale;
-      const float up = (sblk & 1) ? up_odd : up_even;
+        for (int q = 0; q < 4; q++) v[q] = __ldg(xg + sblk * 4 + q);
+        float sum = 0.f, asum = 0.f;
 #pragma unroll
-      for (int q = 0; q < 4; q++) {
-        const uint4 v = __ldg(xg + sblk * 4 + q);   // raw words (x[4i], x[4i+1]), (x[4i+2], x[4i+3]), i = 2q, 2q+1
-        __nv_bfloat162 p0 = __floats2bfloat162_rn(bf16lo(v.x) * up, bf16lo(v.y) * up);
-        __nv_bfloat162 p1 = __floats2bfloat162_rn(bf16hi(v.x) * up, bf16hi(v.y) * up);
-        __nv_bfloat162 p2 = __floats2bfloat162_rn(bf16lo(v.z) * up, bf16lo(v.w) * up);
-        __nv_bfloat162 p3 = __floats2bfloat162_rn(bf16hi(v.z) * up, bf16hi(v.w) * up);
-        xv[sblk * 4 + q] = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
-                                      *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+        for (int q = 0; q < 4; q++) {
+          // raw words (x[4i], x[4i+1]), (x[4i+2], x[4i+3]), i = 2q, 2q+1
+          const float e0 = bf16lo(v[q].x), e1 = bf16hi(v[q].x), e2 = bf16lo(v[q].y), e3 = bf16hi(v[q].y);
+          const float e4 = bf16lo(v[q].z), e5 = bf16hi(v[q].z), e6 = bf16lo(v[q].w), e7 = bf16hi(v[q].w);
+          sum += (e0 + e1) + (e2 + e3) + ((e4 + e5) + (e6 + e7));
+          asum += (fabsf(e0) + fabsf(e1)) + (fabsf(e2) + fabsf(e3)) + ((fabsf(e4) + fabsf(e5)) + (fabsf(e6) + fabsf(e7)));
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(e0 * up, e2 * up);
+          __nv_bfloat162 p1 = __floats2bfloat162_rn(e1 * up, e3 * up);
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(e4 * up, e6 * up);
+          __nv_bfloat162 p3 = __floats2bfloat162_rn(e5 * up, e7 * up);
+          xv[sblk * 4 + q] = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                                        *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+        }
+        xs[sblk] = sum * xs_scale;
+        amax = fmaxf(amax, asum);
       }
-    }
+      return amax;
+    };
+    // Optimistic scale 2^96: right whenever the largest |x| lies in about [2^-30, 2^24), i.e. for
+    // any sane activation tensor.  Otherwise the tensor is staged a second time with a scale that
+    // puts its largest magnitude near 2^120 (S limited to 8..120, which covers largest magnitudes
+    // from about 2^-80 to 2^112 at full precision; beyond that the products over- or underflow).
+    // The magnitude is judged from the largest sub-block sum of |x| (cheap: one add per element),
+    // which overestimates the largest |x| by at most a factor 32.
+    S = 96;
+    atomicMax(xmax, (int)__float_as_uint(stage_x(S)));    // non-negative floats order like integers
     __syncthreads();
+    const int emax = min((*xmax >> 23) & 0xFF, 254);       // biased exponent of that bound (NaN/inf: 255)
+    if (emax > 156 || emax < 97) {
+      S = max(8, min(120, 247 - emax));
+      stage_x(S);
+      __syncthreads();
+    }
   }
   const float d_up = __uint_as_float((uint32_t)(127 + 133 - S) << 23);   // 2^(133-S)
   const bool live = (g >> 1) == t;
@@ -309,6 +350,15 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
   const uint32_t xs_lane_base = smem_u32(xs) + 8 * t;
   const LaneScale lc(t);
   float* red = reinterpret_cast<float*>(smem + L.red(K));
+
+  // One output value: locally, or into every rank's copy of the full output when row-sharded.
+  auto emit = [&](int row, float v) {
+    if (pp.world == 0) {
+      store_out(y, y_dtype, row, v);
+    } else {
+      for (int p = 0; p < pp.world; p++) store_out(pp.y[p], y_dtype, pp.row_offset + row, v);
+    }
+  };
 
   // ---- multiply side: walk my units row group by row group ----
   int rg = rg_begin, c = c_begin, done = 0, slot = 0, flush_parity = 0;
@@ -364,7 +414,7 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
 #pragma unroll
         for (int h = 0; h < 2; h++) {
           const int r = lane + 32 * h, row = rg * kRowsPerUnit + r;
-          if (r < kRowsPerUnit && row < N) store_out(y, y_dtype, row, v[h]);
+          if (r < kRowsPerUnit && row < N) emit(row, v[h]);
         }
       } else {
         const int slot_p = (rg == rg_begin) ? 0 : 1;
@@ -387,8 +437,8 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
             s1 += __ldcg(&theirs[lane + 32]);
           }
           const int row0 = rg * kRowsPerUnit + lane, row1 = row0 + 32;
-          if (row0 < N) store_out(y, y_dtype, row0, s0);
-          if (lane + 32 < kRowsPerUnit && row1 < N) store_out(y, y_dtype, row1, s1);
+          if (row0 < N) emit(row0, s0);
+          if (lane + 32 < kRowsPerUnit && row1 < N) emit(row1, s1);
           if (lane == 0) counters[rg] = 0;
         }
       }
@@ -396,6 +446,25 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
     if (c == C) { c = 0; ++rg; }
   }
   cp_async_wait<0>();
+  if (pp.world > 0) {
+    // Publish: once every CTA of this launch has pushed its rows to the peers, raise this rank's
+    // flag everywhere.  fence -> counter -> (last CTA) fence -> flag stores orders all the data
+    // stores of the grid before the flag as seen from any GPU.
+    __syncthreads();
+    if (tid == 0) {
+      uint32_t* mine = pp.flags[pp.rank];
+      __threadfence_system();
+      const uint32_t done = atomicAdd(mine + pp.world + 1, 1u);
+      if (done == (uint32_t)G - 1) {
+        mine[pp.world + 1] = 0;
+        const uint32_t epoch = mine[pp.world] + 1;
+        mine[pp.world] = epoch;
+        __threadfence_system();
+        for (int p = 0; p < pp.world; p++)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pp.flags[p] + pp.rank), "r"(epoch) : "memory");
+      }
+    }
+  }
 }
 
 }  // namespace q4k
@@ -418,9 +487,10 @@ size_t gemv_q4k_workspace_bytes(int64_t N, int sm_count) {
 }
 
 cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void* y, int y_dtype, void* ws,
-                     size_t ws_bytes, int sm_count, int* status, cudaStream_t st) {
+                     size_t ws_bytes, int sm_count, int* status, cudaStream_t st, const PeerPublish* peers) {
   using namespace q4k;
-  (void)status;
+  PeerPublish pp = {};
+  if (peers) pp = *peers;
   if (ws_bytes < gemv_q4k_workspace_bytes(N, sm_count) || !ws) return cudaErrorInvalidValue;
   const int64_t RG = (N + kRowsPerUnit - 1) / kRowsPerUnit;
   const int SB = (int)(K / 256);
@@ -444,9 +514,9 @@ cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
   int* counters = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ws) + kPartialBytes);
   if (sm_count > kMaxSmCount) return cudaErrorInvalidValue;
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
-  if (depth == 4) gemv_q4k_m1_kernel<4><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
-  else if (depth == 3) gemv_q4k_m1_kernel<3><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
-  else gemv_q4k_m1_kernel<2><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
+  if (depth == 4) gemv_q4k_m1_kernel<4><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
+  else if (depth == 3) gemv_q4k_m1_kernel<3><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
+  else gemv_q4k_m1_kernel<2><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
   return cudaPeekAtLastError();
 }
 

@@ -13,10 +13,10 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
-from . import _matmul
+from . import _backend, _lib, _matmul
 from .array import QuantizedArray
 
-__all__ = ["row_range", "shard_rows", "sharded_matmul", "gather_columns"]
+__all__ = ["row_range", "shard_rows", "sharded_matmul", "gather_columns", "PeerOutput"]
 
 
 def row_range(n_rows: int, rank: int, world: int) -> tuple[int, int]:
@@ -64,3 +64,76 @@ def gather_columns(y_local: torch.Tensor, group=None, out: torch.Tensor | None =
 def sharded_matmul(x: torch.Tensor, w_shard: QuantizedArray, group=None, **kw) -> torch.Tensor:
     """``x @ w.T`` for a row-sharded ``w``: local fused multiply, then the all-gather."""
     return gather_columns(_matmul.matmul(x, w_shard, **kw), group)
+
+
+class PeerOutput:
+    """Replicated output buffers that the fused kernels fill on every rank at once.
+
+    Instead of ``y_local`` followed by an all-gather, :meth:`matmul` launches the kernel behind
+    ``ggq_gemv_sharded``: it stores this rank's slice of the output rows straight into every
+    rank's copy of ``y`` through peer-mapped pointers (NVLink), and raises a per-rank flag on all
+    ranks when its grid has finished.  A following :meth:`matmul` (with ``wait_previous=True``)
+    begins by waiting for everybody's flag, so a chain of sharded layers needs no collective
+    call and no host synchronisation between layers.
+
+    The buffers live in symmetric memory (``torch.distributed._symmetric_memory``), which provides
+    the peer mappings; two output buffers alternate so that a rank that runs ahead never
+    overwrites activations a slower rank is still reading.
+    """
+
+    def __init__(self, group, max_batch: int, n_total: int, dtype=torch.bfloat16, device=None, n_buffers: int = 2):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one NVLink domain)")
+        self.device = torch.device(device) if device is not None else _backend.default_device()
+        self.dtype = _backend.canon_dtype(dtype)
+        self.n_total = int(n_total)
+        self.max_batch = int(max_batch)
+        self._bufs, self._buf_ptrs = [], []
+        for _ in range(n_buffers):
+            t = symm.empty((self.max_batch, self.n_total), dtype=self.dtype, device=self.device)
+            hdl = symm.rendezvous(t, self.group)
+            self._bufs.append(t)
+            self._buf_ptrs.append((ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs]))
+        flags = symm.empty((64,), dtype=torch.int32, device=self.device)
+        flags.zero_()
+        hdl = symm.rendezvous(flags, self.group)
+        self._flags = flags
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
+        self._turn = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def matmul(self, x: torch.Tensor, w_shard: QuantizedArray, wait_previous: bool = True) -> torch.Tensor:
+        """Launch the fused multiply + exchange; returns this rank's ``(M, n_total)`` buffer.  Its
+        contents are complete once every rank's launch has finished (the next fused launch waits for
+        that on the device; host code must synchronise and pass a barrier before reading it)."""
+        if len(w_shard.shape) != 2 or x.shape[-1] != w_shard.shape[1]:
+            raise ValueError(f"contraction mismatch: x {tuple(x.shape)}, w {w_shard.shape}")
+        if w_shard.shape[0] * self.world != self.n_total:
+            raise ValueError(f"{self.world} shards of {w_shard.shape[0]} rows do not make {self.n_total}")
+        k = w_shard.shape[1]
+        xm = x.reshape(-1, k).contiguous()
+        m = xm.shape[0]
+        if m > self.max_batch:
+            raise ValueError(f"batch {m} exceeds the buffers' {self.max_batch}")
+        dev = _backend.require_cuda(w_shard.data, "sharded matmul")
+        _lib.ensure_tables(dev)
+        L = _lib.lib()
+        turn = self._turn
+        self._turn = (turn + 1) % len(self._bufs)
+        with torch.cuda.device(dev):
+            ws = _backend.workspace(dev, L.ggq_workspace_bytes(int(w_shard.qtype), w_shard.shape[0], k, m))
+            _lib.check(L.ggq_gemv_sharded(
+                int(w_shard.qtype), w_shard.data.data_ptr(), w_shard.shape[0], k, xm.data_ptr(), m,
+                self._buf_ptrs[turn], self._flag_ptrs, self.world, self.rank, self.n_total,
+                _backend.dtype_code(self.dtype), 1 if wait_previous else 0,
+                ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                _backend.stream_ptr(dev)))
+        return self._bufs[turn][:m]

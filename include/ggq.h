@@ -107,6 +107,23 @@ int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, const void*
                  int32_t M, void* y, int32_t y_dtype, void* workspace,
                  size_t workspace_bytes, void* stream);
 
+/* Row-sharded multiply with the exchange fused into the kernel.  No counterpart in the reference
+ * (it runs on one device only); it stands where a sharded caller would otherwise follow ggq_gemv
+ * with an all-gather.  `w` holds this rank's N_local rows of an (world * N_local, K) weight;
+ * y_peers[p] is the address, valid on THIS device, of rank p's full (M, n_total) output buffer
+ * (peer-mapped over NVLink for p != rank), flag_peers[p] likewise of rank p's flag array of
+ * world + 2 uint32, zero-filled once.  The kernel stores its rows into every rank's buffer with
+ * plain stores and, when its grid has finished, raises its flag on every rank.  With
+ * wait_previous != 0 it first waits (bounded; GGQ_TIMEOUT through ggq_read_status) until every
+ * rank has published the previous exchange, i.e. until x -- if it is the result of that exchange
+ * -- is complete.  All ranks must issue the same sequence of calls.  Host arrays y_peers /
+ * flag_peers are read during the call only.  Returns GGQ_UNSUPPORTED for qtype / batch
+ * combinations without a publishing kernel (today: everything but Q4_K at batch 1). */
+int32_t ggq_gemv_sharded(int32_t qtype, const void* w, int64_t N_local, int64_t K, const void* x_bf16,
+                         int32_t M, void* const* y_peers, uint32_t* const* flag_peers, int32_t world,
+                         int32_t rank, int64_t n_total, int32_t y_dtype, int32_t wait_previous,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
 /* Batch-1 Q4_K multiply that needs no scratch from the caller and allocates nothing.
  * No counterpart in the reference.  It exists for hosts that cannot allocate device memory
  * around a call: a custom-call handler whose framework owns every buffer, code between

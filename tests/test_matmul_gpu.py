@@ -258,3 +258,22 @@ def test_router_uses_the_tensor_core_kernel_between_the_caps():
     x = to_x(synth.make_x(cap, 512, seed=5))
     ref = O.c_matmul(O.bf16_bits(x.float().cpu().numpy()), w.data.cpu().numpy(), QT.Q4_K)
     check_close(gj.matmul(x, w).float().cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("log2_scale", [-70, -40, -20, 0, 25, 35, 70, 110])
+def test_q4k_batch1_kernel_activation_magnitudes(log2_scale):
+    """The kernel rescales the activations by a power of two internally; the result must not
+    depend on their magnitude (a second staging pass handles tensors far from unit scale)."""
+    n, k = 256, 1024
+    w = synth.make_weight_bytes(n, k, QT.Q4_K, seed=8)
+    x = synth.make_x(1, k, seed=9) * np.float32(2.0 ** log2_scale)
+    ref = O.c_matmul(O.bf16_bits(x), w, QT.Q4_K)
+    got = run_fused(x, w, QT.Q4_K, torch.float32)
+    assert np.isfinite(got).all()
+    assert O.rel_l2(got, ref) <= 2e-5, O.rel_l2(got, ref)
+
+
+def test_q4k_batch1_kernel_zero_activations():
+    w = synth.make_weight_bytes(64, 512, QT.Q4_K, seed=1)
+    got = run_fused(np.zeros((1, 512), np.float32), w, QT.Q4_K, torch.float32)
+    assert (got == 0).all()
