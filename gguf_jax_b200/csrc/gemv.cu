@@ -7,8 +7,10 @@ namespace {
 constexpr int kGemvMaxBatch = 16;
 // From this batch on the tensor-core small-batch kernel beats the per-element FMA kernel.
 constexpr int kMmaMinBatch = 2;
-// Above this batch the dequantize-then-GEMM route (decode kernel + library bf16 GEMM) wins.
-constexpr int kGemmMaxBatch = 256;
+// Measured on B200 the tcgen05 kernel behind ggq_gemm is still slower than the decode kernel
+// followed by a library bf16 GEMM (its producers wait on global loads), so
+// ggq_fused_batch_limit keeps the router at the small-batch cap and ggq_gemm is reached only
+// by name.
 }
 
 extern "C" int32_t ggq_gemv_max_batch(void) { return kGemvMaxBatch; }
@@ -16,7 +18,7 @@ extern "C" int32_t ggq_gemv_max_batch(void) { return kGemvMaxBatch; }
 extern "C" int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K) {
   const TypeInfo* ti = type_info(qtype);
   if (!ti || !ti->fused || N <= 0 || K <= 0 || K % ti->block_elems) return 0;
-  return gemm_applicable(ti, N, K, kGemmMaxBatch) ? kGemmMaxBatch : kGemvMaxBatch;
+  return kGemvMaxBatch;
 }
 
 static int sm_count_of(int dev) {
@@ -27,9 +29,17 @@ static int sm_count_of(int dev) {
 }
 
 extern "C" size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32_t M) {
-  (void)K; (void)M;
-  if (qtype == QT_Q4_K && N > 0) return gemv_q4k_workspace_bytes(N, kMaxSmCount);
-  return 0;
+  const TypeInfo* ti = type_info(qtype);
+  if (!ti || N <= 0 || K <= 0) return 0;
+  size_t need = 0;
+  if (qtype == QT_Q4_K) need = gemv_q4k_workspace_bytes(N, kMaxSmCount);
+  if (M > kGemvMaxBatch && gemm_applicable(ti, N, K, M)) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) { dev = -1; (void)cudaGetLastError(); }
+    const size_t g = gemm_workspace_bytes(N, K, M, sm_count_of(dev));
+    if (g > need) need = g;
+  }
+  return need;
 }
 
 extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
@@ -123,7 +133,6 @@ extern "C" int32_t ggq_gemv_q4k_static(const void* w, int64_t N, int64_t K, cons
 extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
                             int32_t M, void* y, int32_t y_dtype, void* workspace, size_t workspace_bytes,
                             void* stream) {
-  (void)workspace; (void)workspace_bytes;
   const TypeInfo* ti = type_info(qtype);
   if (!ti) return fail(GGQ_BAD_QTYPE, "ggq_gemm: qtype %d is not decodable", qtype);
   if (!ti->fused) return fail(GGQ_UNSUPPORTED, "ggq_gemm: no fused kernel for qtype %d", qtype);
@@ -145,7 +154,7 @@ extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, 
   if (ti->needs_tables && !tab)
     return fail(GGQ_NO_TABLES, "ggq_gemm: call ggq_set_tables(%d, ...) before using qtype %d", dev, qtype);
   cudaError_t err = gemm_tf32(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, device_status_word(dev),
-                              (cudaStream_t)stream);
+                              workspace, workspace_bytes, sm_count_of(dev), (cudaStream_t)stream);
   if (err != cudaSuccess) return fail(GGQ_LAUNCH_FAILED, "ggq_gemm: %s", cudaGetErrorString(err));
   return GGQ_OK;
 }

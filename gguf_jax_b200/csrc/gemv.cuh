@@ -58,8 +58,16 @@ cudaError_t gemv_mma(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K,
 
 // Larger batches: tcgen05 / TMEM tensor-core kernel with tf32 operands (gemm_tcgen05.cu).
 bool gemm_applicable(const TypeInfo* ti, int64_t N, int64_t K, int M);
+int gemm_splits(int64_t N, int64_t K, int M, int sm_count);
+size_t gemm_workspace_bytes(int64_t N, int64_t K, int M, int sm_count);
 cudaError_t gemm_tf32(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y,
-                      int y_dtype, const uint8_t* tab, int* status, cudaStream_t st);
+                      int y_dtype, const uint8_t* tab, int* status, void* ws, size_t ws_bytes, int sm_count,
+                      cudaStream_t st);
+
+// Fixed offsets inside the caller's scratch: GEMV partial slots first, then the arrival counters
+// of every kernel (each launch leaves them at zero), then the float32 partial tiles of the GEMM.
+constexpr size_t kWsCounterOffset = (size_t)256 * 2 * 64 * sizeof(float);   // 128 KB
+constexpr size_t kWsGemmPartialOffset = (size_t)4 << 20;
 
 // Upper bound on the SM count used when sizing scratch (the kernels use the real count).
 constexpr int kMaxSmCount = 256;

@@ -471,7 +471,7 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
 
 bool gemv_q4k_applicable(int64_t N, int64_t K, int M, const void* w, const void* x) {
   return M == 1 && K % 256 == 0 && q4k::Smem(2).total((int)K) <= q4k::kSmemLimit && N >= 1 &&
-         N < (1ll << 31) - 64 && N * (K / 256 * 144) < (1ll << 40) && (uintptr_t)w % 16 == 0 && (uintptr_t)x % 16 == 0;
+         N <= (1ll << 24) && N * (K / 256 * 144) < (1ll << 40) && (uintptr_t)w % 16 == 0 && (uintptr_t)x % 16 == 0;
 }
 
 // Scratch layout: [partial slots: kMaxSmCount CTAs x 2 x 64 floats][arrival counters: one int per
@@ -479,6 +479,7 @@ bool gemv_q4k_applicable(int64_t N, int64_t K, int M, const void* w, const void*
 // call, whatever its shape, live in bytes that only ever hold counters (which each launch leaves
 // at zero); partial slots may hold stale floats, they are always written before they are read.
 static constexpr size_t kPartialBytes = (size_t)kMaxSmCount * 2 * 64 * sizeof(float);
+static_assert(kPartialBytes == kWsCounterOffset, "the counters of every kernel share one area");
 
 size_t gemv_q4k_workspace_bytes(int64_t N, int sm_count) {
   (void)sm_count;

@@ -101,8 +101,11 @@ int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, const void*
                  int32_t M, void* y, int32_t y_dtype, void* workspace,
                  size_t workspace_bytes, void* stream);
 
-/* Same product for larger M on the tcgen05 tensor-core path.
- * Replaces gemm_q4_k (src/gguf_jax/cute/q4_k_gemm.py:369-391). */
+/* Same product for larger M on the tcgen05 tensor-core path (any block qtype, K a multiple of
+ * 32).  Replaces gemm_q4_k (src/gguf_jax/cute/q4_k_gemm.py:369-391).  With few row tiles the
+ * launch cuts K into ranges and needs ggq_workspace_bytes(qtype, N, K, M) of scratch; without
+ * it (NULL / too small) it runs one range per tile.  ggq_fused_batch_limit does not count this
+ * kernel while it is slower than decode + library GEMM: callers pick it by name. */
 int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
                  int32_t M, void* y, int32_t y_dtype, void* workspace,
                  size_t workspace_bytes, void* stream);

@@ -251,13 +251,32 @@ def test_tensor_core_gemm_one_hot_columns():
     np.testing.assert_allclose(got, want, rtol=2.0 ** -11, atol=0)
 
 
-def test_router_uses_the_tensor_core_kernel_between_the_caps():
+def test_tensor_core_gemm_split_k_is_deterministic_and_leaves_scratch_clean():
+    """Few row tiles: the launch cuts K into ranges and the last CTA of a tile adds the partial
+    tiles.  Same bits every time, and the batch-1 kernel (which shares the counter area of the
+    scratch) still works in between."""
+    n, k, m = 512, 16 * 256, 48
+    w = synth.make_weight_bytes(n, k, QT.Q4_K, seed=21)
+    x = synth.make_x(m, k, seed=22)
+    ref = O.c_matmul(O.bf16_bits(x), w, QT.Q4_K)
+    first = run_fused(x, w, QT.Q4_K, torch.float32)
+    assert O.rel_l2(first, ref) <= 1e-3
+    x1 = synth.make_x(1, k, seed=23)
+    ref1 = O.c_matmul(O.bf16_bits(x1), w, QT.Q4_K)
+    for _ in range(3):
+        assert O.rel_l2(run_fused(x1, w, QT.Q4_K, torch.float32), ref1) <= 2e-5
+        again = run_fused(x, w, QT.Q4_K, torch.float32)
+        assert (again.view(np.uint32) == first.view(np.uint32)).all()
+
+
+def test_router_cap_and_fallback_above_it():
     w = synth.make_weight(256, 512, QT.Q4_K, seed=5)
     cap = gj.fused_batch_limit(w)
-    assert cap > kernels.gemv_max_batch()
-    x = to_x(synth.make_x(cap, 512, seed=5))
-    ref = O.c_matmul(O.bf16_bits(x.float().cpu().numpy()), w.data.cpu().numpy(), QT.Q4_K)
-    check_close(gj.matmul(x, w).float().cpu().numpy(), ref)
+    assert cap == kernels.gemv_max_batch()
+    for m in (cap, cap + 1):
+        x = to_x(synth.make_x(m, 512, seed=5))
+        ref = O.c_matmul(O.bf16_bits(x.float().cpu().numpy()), w.data.cpu().numpy(), QT.Q4_K)
+        check_close(gj.matmul(x, w).float().cpu().numpy(), ref)
 
 
 @pytest.mark.parametrize("log2_scale", [-70, -40, -20, 0, 25, 35, 70, 110])
