@@ -211,6 +211,59 @@ def test_q4k_scratch_is_reusable_across_shapes():
         assert O.rel_l2(run_fused(x, w, QT.Q4_K, torch.float32), ref) <= 2e-5, (n, k)
 
 
+# ---- the tuned Q6_K batch-1 kernel (rows must start 16-byte aligned: K a multiple of 2048) ----
+
+@pytest.mark.parametrize("n,k", [(1, 2048), (3, 2048), (33, 4096), (200, 6144), (4100, 2048), (512, 28672),
+                                 (1024, 8192), (148 * 32, 4096), (5000, 2048), (32, 2048), (31, 4096)])
+def test_q6k_batch1_kernel_shapes(n, k):
+    w = synth.make_weight_bytes(n, k, QT.Q6_K, seed=n + k)
+    x = synth.make_x(1, k, seed=n)
+    ref = O.c_matmul(O.bf16_bits(x), w, QT.Q6_K)
+    got32 = run_fused(x, w, QT.Q6_K, torch.float32)
+    assert O.rel_l2(got32, ref) <= 2e-5, (n, k, O.rel_l2(got32, ref))
+    got16 = run_fused(x, w, QT.Q6_K)
+    assert np.array_equal(got16, torch.from_numpy(got32).to(torch.bfloat16).float().numpy())
+    check_close(got16, ref)
+
+
+def test_q6k_batch1_kernel_one_hot_every_position_of_a_superblock():
+    """x = e_k returns column k of the decoded weight exactly, for every k of one superblock of
+    every alignment class (the block's offset in its 16-byte window is 2 j mod 16)."""
+    n, k = 40, 2048
+    w = synth.make_weight_bytes(n, k, QT.Q6_K, seed=77)
+    W = O.ref_dequantize(w, QT.Q6_K)
+    for col in list(range(0, 256)) + [256 * j + 31 * j + 5 for j in range(1, 8)]:
+        x = np.zeros((1, k), dtype=np.float32)
+        x[0, col] = 1.0
+        got = run_fused(x, w, QT.Q6_K, torch.float32)
+        assert np.array_equal(got[0], W[:, col]), col
+
+
+def test_q6k_batch1_kernel_is_deterministic_and_shares_scratch_with_q4k():
+    first = {}
+    for rep in range(3):
+        for qt, n, k in [(QT.Q6_K, 8192, 2048), (QT.Q4_K, 4100, 1024), (QT.Q6_K, 200, 6144), (QT.Q6_K, 4736, 4096)]:
+            w = synth.make_weight_bytes(n, k, qt, seed=1)
+            x = synth.make_x(1, k, seed=2)
+            got = run_fused(x, w, qt, torch.float32)
+            if rep == 0:
+                first[(qt, n, k)] = got
+                assert O.rel_l2(got, O.c_matmul(O.bf16_bits(x), w, qt)) <= 2e-5
+            else:
+                assert np.array_equal(got.view(np.uint32), first[(qt, n, k)].view(np.uint32))
+
+
+@pytest.mark.parametrize("log2_scale", [-70, -20, 0, 35, 110])
+def test_q6k_batch1_kernel_activation_magnitudes(log2_scale):
+    n, k = 256, 2048
+    w = synth.make_weight_bytes(n, k, QT.Q6_K, seed=8)
+    x = synth.make_x(1, k, seed=9) * np.float32(2.0 ** log2_scale)
+    ref = O.c_matmul(O.bf16_bits(x), w, QT.Q6_K)
+    got = run_fused(x, w, QT.Q6_K, torch.float32)
+    assert np.isfinite(got).all()
+    assert O.rel_l2(got, ref) <= 2e-5, O.rel_l2(got, ref)
+
+
 # ---- the tcgen05 / TMEM kernel for larger batches (tf32 operands, float32 accumulation) ----
 
 GEMM_TYPES = [QT.Q4_K, QT.Q5_K, QT.Q6_K, QT.IQ4_XS, QT.Q8_0, QT.IQ2_XS, QT.Q2_K]
