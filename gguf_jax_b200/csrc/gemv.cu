@@ -32,7 +32,7 @@ extern "C" size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32
   const TypeInfo* ti = type_info(qtype);
   if (!ti || N <= 0 || K <= 0) return 0;
   size_t need = 0;
-  if (qtype == QT_Q4_K || qtype == QT_Q6_K) need = gemv_q4k_workspace_bytes(N, kMaxSmCount);
+  if (qtype == QT_Q4_K || qtype == QT_Q5_K || qtype == QT_Q6_K) need = gemv_q4k_workspace_bytes(N, kMaxSmCount);
   if (M > kGemvMaxBatch && gemm_applicable(ti, N, K, M)) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess) { dev = -1; (void)cudaGetLastError(); }
@@ -71,6 +71,10 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
       sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount) {
     err = gemv_q4k((const uint8_t*)w, N, K, x_bf16, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev),
                    device_status_word(dev), st);
+  } else if (qtype == QT_Q5_K && gemv_q5k_applicable(N, K, M, w, x_bf16) && workspace &&
+             workspace_bytes >= gemv_q4k_workspace_bytes(N, kMaxSmCount) && (uintptr_t)workspace % 256 == 0 &&
+             sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount) {
+    err = gemv_q5k((const uint8_t*)w, N, K, x_bf16, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev), st);
   } else if (qtype == QT_Q6_K && gemv_q6k_applicable(N, K, M, w, x_bf16) && workspace &&
              workspace_bytes >= gemv_q4k_workspace_bytes(N, kMaxSmCount) && (uintptr_t)workspace % 256 == 0 &&
              sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount) {

@@ -51,6 +51,11 @@ bool gemv_q6k_applicable(int64_t N, int64_t K, int M, const void* w, const void*
 cudaError_t gemv_q6k(const uint8_t* w, int64_t N, int64_t K, const void* x, void* y, int y_dtype, void* ws,
                      size_t ws_bytes, int sm_count, cudaStream_t st);
 
+// Q5_K, batch 1: the Q4_K design plus a fifth-bit plane (gemv_q5k.cu).  Scratch as for Q4_K.
+bool gemv_q5k_applicable(int64_t N, int64_t K, int M, const void* w, const void* x);
+cudaError_t gemv_q5k(const uint8_t* w, int64_t N, int64_t K, const void* x, void* y, int y_dtype, void* ws,
+                     size_t ws_bytes, int sm_count, cudaStream_t st);
+
 // Same kernel with the scratch in a file-scope device array (no caller buffer); returns a ggq_status.
 int32_t gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x, void* y, int32_t y_dtype,
                         int sm_count, cudaStream_t st);

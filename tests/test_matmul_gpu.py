@@ -211,6 +211,45 @@ def test_q4k_scratch_is_reusable_across_shapes():
         assert O.rel_l2(run_fused(x, w, QT.Q4_K, torch.float32), ref) <= 2e-5, (n, k)
 
 
+# ---- the tuned Q5_K batch-1 kernel ----
+
+@pytest.mark.parametrize("n,k", [(1, 256), (3, 512), (33, 9 * 256), (200, 11 * 256), (4100, 1024), (20_000, 256),
+                                 (512, 28672), (1024, 8192), (148 * 32, 4096), (5000, 7 * 256)])
+def test_q5k_batch1_kernel_shapes(n, k):
+    w = synth.make_weight_bytes(n, k, QT.Q5_K, seed=n + k)
+    x = synth.make_x(1, k, seed=n)
+    ref = O.c_matmul(O.bf16_bits(x), w, QT.Q5_K)
+    got32 = run_fused(x, w, QT.Q5_K, torch.float32)
+    assert O.rel_l2(got32, ref) <= 2e-5, (n, k, O.rel_l2(got32, ref))
+    got16 = run_fused(x, w, QT.Q5_K)
+    assert np.array_equal(got16, torch.from_numpy(got32).to(torch.bfloat16).float().numpy())
+    check_close(got16, ref)
+
+
+def test_q5k_batch1_kernel_one_hot_every_position_of_a_superblock():
+    n, k = 40, 768
+    w = synth.make_weight_bytes(n, k, QT.Q5_K, seed=78)
+    W = O.ref_dequantize(w, QT.Q5_K)
+    for col in list(range(256, 512)) + [3, 700]:
+        x = np.zeros((1, k), dtype=np.float32)
+        x[0, col] = 1.0
+        got = run_fused(x, w, QT.Q5_K, torch.float32)
+        assert np.array_equal(got[0], W[:, col]), col
+
+
+def test_q5k_batch1_kernel_is_deterministic():
+    first = {}
+    for rep in range(3):
+        for n, k in [(8192, 2048), (200, 11 * 256), (4100, 1024)]:
+            w = synth.make_weight_bytes(n, k, QT.Q5_K, seed=1)
+            x = synth.make_x(1, k, seed=2)
+            got = run_fused(x, w, QT.Q5_K, torch.float32)
+            if rep == 0:
+                first[(n, k)] = got
+            else:
+                assert np.array_equal(got.view(np.uint32), first[(n, k)].view(np.uint32))
+
+
 # ---- the tuned Q6_K batch-1 kernel (rows must start 16-byte aligned: K a multiple of 2048) ----
 
 @pytest.mark.parametrize("n,k", [(1, 2048), (3, 2048), (33, 4096), (200, 6144), (4100, 2048), (512, 28672),
