@@ -368,7 +368,11 @@ def test_router_cap_and_fallback_above_it():
     for m in (cap, cap + 1):
         x = to_x(synth.make_x(m, 512, seed=5))
         ref = O.c_matmul(O.bf16_bits(x.float().cpu().numpy()), w.data.cpu().numpy(), QT.Q4_K)
-        check_close(gj.matmul(x, w).float().cpu().numpy(), ref)
+        got = gj.matmul(x, w).float().cpu().numpy()
+        if m <= cap:
+            check_close(got, ref)
+        else:   # decode to bf16 + library GEMM: the reference's own tolerance for that route
+            np.testing.assert_allclose(got, ref, rtol=2e-2, atol=2e-2 * np.abs(ref).max())
 
 
 @pytest.mark.parametrize("log2_scale", [-70, -40, -20, 0, 25, 35, 70, 110])
