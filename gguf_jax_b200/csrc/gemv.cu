@@ -74,11 +74,13 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
   } else if (qtype == QT_Q5_K && gemv_q5k_applicable(N, K, M, w, x_bf16) && workspace &&
              workspace_bytes >= gemv_q4k_workspace_bytes(N, kMaxSmCount) && (uintptr_t)workspace % 256 == 0 &&
              sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount) {
-    err = gemv_q5k((const uint8_t*)w, N, K, x_bf16, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev), st);
+    err = gemv_q5k((const uint8_t*)w, N, K, x_bf16, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev),
+                   device_status_word(dev), st);
   } else if (qtype == QT_Q6_K && gemv_q6k_applicable(N, K, M, w, x_bf16) && workspace &&
              workspace_bytes >= gemv_q4k_workspace_bytes(N, kMaxSmCount) && (uintptr_t)workspace % 256 == 0 &&
              sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount) {
-    err = gemv_q6k((const uint8_t*)w, N, K, x_bf16, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev), st);
+    err = gemv_q6k((const uint8_t*)w, N, K, x_bf16, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev),
+                   device_status_word(dev), st);
   } else if (gemv_mma_applicable(ti, N, K, M) && M >= kMmaMinBatch) {
     err = gemv_mma(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, st);
   } else {
@@ -104,9 +106,12 @@ extern "C" int32_t ggq_gemv_sharded(int32_t qtype, const void* w, int64_t N_loca
   if (!w || !x_bf16 || !y_peers || !flag_peers) return fail(GGQ_MISALIGNED, "ggq_gemv_sharded: null pointer");
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!(qtype == QT_Q4_K && gemv_q4k_applicable(N_local, K, M, w, x_bf16)))
-    return fail(GGQ_UNSUPPORTED, "ggq_gemv_sharded: only the Q4_K batch-1 kernel publishes to peers so far; "
-                "use ggq_gemv plus an all-gather for qtype %d, M=%d", qtype, M);
+  const bool ok4 = qtype == QT_Q4_K && gemv_q4k_applicable(N_local, K, M, w, x_bf16);
+  const bool ok5 = qtype == QT_Q5_K && gemv_q5k_applicable(N_local, K, M, w, x_bf16);
+  const bool ok6 = qtype == QT_Q6_K && gemv_q6k_applicable(N_local, K, M, w, x_bf16);
+  if (!(ok4 || ok5 || ok6))
+    return fail(GGQ_UNSUPPORTED, "ggq_gemv_sharded: only the Q4_K / Q5_K / Q6_K batch-1 kernels publish to peers so "
+                "far; use ggq_gemv plus an all-gather for qtype %d, M=%d, K=%lld", qtype, M, (long long)K);
   if (!workspace || workspace_bytes < gemv_q4k_workspace_bytes(N_local, kMaxSmCount) || (uintptr_t)workspace % 256)
     return fail(GGQ_BAD_WORKSPACE, "ggq_gemv_sharded: workspace of %zu bytes needed", gemv_q4k_workspace_bytes(N_local, kMaxSmCount));
   PeerPublish pp = {};
@@ -120,8 +125,10 @@ extern "C" int32_t ggq_gemv_sharded(int32_t qtype, const void* w, int64_t N_loca
   pp.n_total = n_total;
   pp.row_offset = (int64_t)rank * N_local;
   pp.wait_previous = wait_previous ? 1 : 0;
-  cudaError_t err = gemv_q4k((const uint8_t*)w, N_local, K, x_bf16, nullptr, y_dtype, workspace, workspace_bytes,
-                             sm_count_of(dev), device_status_word(dev), (cudaStream_t)stream, &pp);
+  cudaError_t (*kernel)(const uint8_t*, int64_t, int64_t, const void*, void*, int, void*, size_t, int, int*,
+                        cudaStream_t, const PeerPublish*) = ok4 ? gemv_q4k : ok5 ? gemv_q5k : gemv_q6k;
+  cudaError_t err = kernel((const uint8_t*)w, N_local, K, x_bf16, nullptr, y_dtype, workspace, workspace_bytes,
+                           sm_count_of(dev), device_status_word(dev), (cudaStream_t)stream, &pp);
   if (err != cudaSuccess) return fail(GGQ_LAUNCH_FAILED, "ggq_gemv_sharded: %s", cudaGetErrorString(err));
   return GGQ_OK;
 }

@@ -39,6 +39,64 @@ struct PeerPublish {
   // numbers, and a captured CUDA graph can be replayed.
 };
 
+#ifdef __CUDACC__
+// Consumer side, threads tid < world of one CTA (every CTA does it): the activations were produced
+// by the previous exchange, whose number is this rank's own epoch; wait until every rank has
+// raised its flag here to that number.  Bounded (about 50 ms of wall time); when it runs out the
+// status word is raised and the launch carries on (its result is then meaningless, the host sees
+// GGQ_TIMEOUT).
+__device__ __forceinline__ void peer_wait_previous(const PeerPublish& pp, int tid, int* status) {
+  if (pp.world > 0 && pp.wait_previous && tid < pp.world) {
+    const uint32_t* mine = pp.flags[pp.rank];
+    const uint32_t target = mine[pp.world];
+    bool ok = false;
+    uint64_t t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (uint32_t i = 0; i < (1u << 26) && !ok; i++) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + tid) : "memory");
+      ok = (int32_t)(v - target) >= 0;
+      if (!ok && (i & 63) == 63) {
+        uint64_t t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > 50000000ull) break;
+      }
+    }
+    if (!ok && status) atomicOr(status, STATUS_WAIT_EXPIRED);
+  }
+}
+// One output value: locally, or into every rank's copy of the full output when row-sharded.
+__device__ __forceinline__ void peer_emit(const PeerPublish& pp, void* y, int y_dtype, int64_t row, float v) {
+  if (pp.world == 0) {
+    store_out(y, y_dtype, row, v);
+  } else {
+    for (int p = 0; p < pp.world; p++) store_out(pp.y[p], y_dtype, pp.row_offset + row, v);
+  }
+}
+// Producer side, called by every thread of every CTA at the end of the kernel: once every CTA of
+// the launch has pushed its rows to the peers, raise this rank's flag everywhere.
+// fence -> counter -> (last CTA) fence -> flag stores orders all the data stores of the grid
+// before the flag as seen from any GPU.
+__device__ __forceinline__ void peer_publish(const PeerPublish& pp, int tid, int n_ctas) {
+  if (pp.world > 0) {
+    __syncthreads();
+    if (tid == 0) {
+      uint32_t* mine = pp.flags[pp.rank];
+      __threadfence_system();
+      const uint32_t done = atomicAdd(mine + pp.world + 1, 1u);
+      if (done == (uint32_t)n_ctas - 1) {
+        mine[pp.world + 1] = 0;
+        const uint32_t epoch = mine[pp.world] + 1;
+        mine[pp.world] = epoch;
+        __threadfence_system();
+        for (int p = 0; p < pp.world; p++)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pp.flags[p] + pp.rank), "r"(epoch) : "memory");
+      }
+    }
+  }
+}
+#endif
+
 // Q4_K, batch 1: cp.async-staged tensor-core kernel (gemv_q4k.cu).
 bool gemv_q4k_applicable(int64_t N, int64_t K, int M, const void* w, const void* x);
 size_t gemv_q4k_workspace_bytes(int64_t N, int sm_count);
@@ -49,12 +107,12 @@ cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
 // Q6_K, batch 1: the same design on 210-byte superblocks (gemv_q6k.cu).  Scratch as for Q4_K.
 bool gemv_q6k_applicable(int64_t N, int64_t K, int M, const void* w, const void* x);
 cudaError_t gemv_q6k(const uint8_t* w, int64_t N, int64_t K, const void* x, void* y, int y_dtype, void* ws,
-                     size_t ws_bytes, int sm_count, cudaStream_t st);
+                     size_t ws_bytes, int sm_count, int* status, cudaStream_t st, const PeerPublish* peers = nullptr);
 
 // Q5_K, batch 1: the Q4_K design plus a fifth-bit plane (gemv_q5k.cu).  Scratch as for Q4_K.
 bool gemv_q5k_applicable(int64_t N, int64_t K, int M, const void* w, const void* x);
 cudaError_t gemv_q5k(const uint8_t* w, int64_t N, int64_t K, const void* x, void* y, int y_dtype, void* ws,
-                     size_t ws_bytes, int sm_count, cudaStream_t st);
+                     size_t ws_bytes, int sm_count, int* status, cudaStream_t st, const PeerPublish* peers = nullptr);
 
 // Same kernel with the scratch in a file-scope device array (no caller buffer); returns a ggq_status.
 int32_t gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x, void* y, int32_t y_dtype,

@@ -1,17 +1,17 @@
 // Q4_K fused decode + multiply for batch 1, tuned for B200 HBM bandwidth.
 //
 // Data movement.  A persistent CTA per SM with sixteen warps.  Every warp streams its own
-// tiles (16 weight rows x one 144-byte superblock, 2304 B) from HBM into a private ring of
-// shared-memory slots with 16-byte cp.async copies, three tiles ahead of the one it is
-// multiplying (about 110 KB in flight per SM, no registers held by loads in flight); the
-// sixteen warps of a CTA sit on adjacent superblocks of the same 32 rows, so each row is
-// read as a contiguous run.  Per-thread cp.async is used rather than TMA on purpose:
-// measured on this part, a ring fed by cp.async.bulk copies of ~1 KB per row stops at
-// 3.4 TB/s (about 50 cycles of fixed cost per bulk copy, one TMA unit per SM) and copies of
-// 16 KB reach 5.7 TB/s, while 16-byte loads issued by all warps stream 5.8-6.4 TB/s.  The
-// GGUF row-major block layout only offers ~1 KB contiguous per row per 16-row tile, so the
-// per-thread copies win.  A tile is stored densely (row pitch 144 B = 16 mod 128), which
-// makes the 128-bit shared-memory reads of the MMA fragment layout bank-conflict free.
+// steps (16 weight rows x two adjacent 144-byte superblocks, 4.6 KB) from HBM into a private
+// ring of shared-memory slots with 16-byte cp.async copies, one to three steps ahead of the
+// one it is multiplying (as many as shared memory allows next to the staged activations; no
+// registers are held by loads in flight); the warps of a CTA sit on adjacent superblocks of
+// the same 32 rows, so each row is read as a contiguous run.  Per-thread cp.async is used
+// rather than TMA on purpose: measured on this part, a ring fed by cp.async.bulk copies of
+// ~1 KB per row stops at 3.4 TB/s (about 50 cycles of fixed cost per bulk copy, one TMA unit
+// per SM) and copies of 16 KB reach 5.7 TB/s, while 16-byte loads issued by all warps stream
+// 5.8-6.4 TB/s.  The GGUF row-major block layout only offers a few hundred contiguous bytes
+// per row per 16-row tile, so the per-thread copies win.  The row pitch of a slot (304 B =
+// 48 mod 128) makes the 128-bit shared-memory reads of the MMA fragment layout conflict free.
 //
 // Arithmetic.  Per-element FMAs cannot keep up with HBM on this part (about 2.5 issued
 // lane-instructions per weight at peak bandwidth), so the dot products run on the tensor
@@ -44,7 +44,8 @@
 // boundary is finished by whichever CTA arrives last: partial sums go to a small scratch
 // buffer, a per-row-group counter tells the last arriver, which adds the partials in CTA
 // order (deterministic) and leaves the counter at zero again.  No thread ever waits on
-// another CTA or on an asynchronous copy, so there is no spin loop in this kernel.
+// another CTA.  The only spin loop is the bounded wait of the row-sharded variant for the
+// peers' flags of the previous exchange (50 ms, then the status word is raised).
 #include "gemv.cuh"
 
 namespace ggq {
@@ -263,29 +264,7 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
     // memory as scaled, pair-permuted bf16: word 2i = (x[4i], x[4i+2]), word 2i+1 = (x[4i+1], x[4i+3]).
     if (tid < 16) reinterpret_cast<uint32_t*>(smem + L.zero(K))[tid] = 0;
     if (tid == 0) *xmax = 0;
-    if (pp.world > 0 && pp.wait_previous && tid < pp.world) {
-      // The activations were produced by the previous exchange, whose number is this rank's own
-      // epoch: wait until every rank has raised its flag here to that number.  Bounded; when it
-      // runs out the status word is raised and the launch carries on (its result is then
-      // meaningless, the host sees GGQ_TIMEOUT).
-      const uint32_t* mine = pp.flags[pp.rank];
-      const uint32_t target = mine[pp.world];
-      // poll for at most ~50 ms of wall time
-      bool ok = false;
-      uint64_t t0;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-      for (uint32_t i = 0; i < (1u << 26) && !ok; i++) {
-        uint32_t v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + tid) : "memory");
-        ok = (int32_t)(v - target) >= 0;
-        if (!ok && (i & 63) == 63) {
-          uint64_t t1;
-          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-          if (t1 - t0 > 50000000ull) break;
-        }
-      }
-      if (!ok && status) atomicOr(status, STATUS_WAIT_EXPIRED);
-    }
+    peer_wait_previous(pp, tid, status);
     __syncthreads();
     const uint4* xg = reinterpret_cast<const uint4*>(x);
     uint4* xv = reinterpret_cast<uint4*>(smem + L.x);
@@ -351,14 +330,7 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
   const LaneScale lc(t);
   float* red = reinterpret_cast<float*>(smem + L.red(K));
 
-  // One output value: locally, or into every rank's copy of the full output when row-sharded.
-  auto emit = [&](int row, float v) {
-    if (pp.world == 0) {
-      store_out(y, y_dtype, row, v);
-    } else {
-      for (int p = 0; p < pp.world; p++) store_out(pp.y[p], y_dtype, pp.row_offset + row, v);
-    }
-  };
+  auto emit = [&](int row, float v) { peer_emit(pp, y, y_dtype, row, v); };
 
   // ---- multiply side: walk my units row group by row group ----
   int rg = rg_begin, c = c_begin, done = 0, slot = 0, flush_parity = 0;
@@ -446,25 +418,7 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
     if (c == C) { c = 0; ++rg; }
   }
   cp_async_wait<0>();
-  if (pp.world > 0) {
-    // Publish: once every CTA of this launch has pushed its rows to the peers, raise this rank's
-    // flag everywhere.  fence -> counter -> (last CTA) fence -> flag stores orders all the data
-    // stores of the grid before the flag as seen from any GPU.
-    __syncthreads();
-    if (tid == 0) {
-      uint32_t* mine = pp.flags[pp.rank];
-      __threadfence_system();
-      const uint32_t done = atomicAdd(mine + pp.world + 1, 1u);
-      if (done == (uint32_t)G - 1) {
-        mine[pp.world + 1] = 0;
-        const uint32_t epoch = mine[pp.world] + 1;
-        mine[pp.world] = epoch;
-        __threadfence_system();
-        for (int p = 0; p < pp.world; p++)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pp.flags[p] + pp.rank), "r"(epoch) : "memory");
-      }
-    }
-  }
+  peer_publish(pp, tid, G);
 }
 
 }  // namespace q4k

@@ -168,7 +168,8 @@ __device__ __forceinline__ void compute_tile(uint32_t blk, int g, int t, const L
 template <int DEPTH>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_q6k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat16* __restrict__ x,
-                   void* __restrict__ y, int y_dtype, int* __restrict__ counters, float* __restrict__ partials) {
+                   void* __restrict__ y, int y_dtype, int* __restrict__ counters, float* __restrict__ partials,
+                   const PeerPublish pp, int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int SB = K / 256;                        // superblocks per row (a multiple of 8)
@@ -237,6 +238,7 @@ gemv_q6k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
   {
     if (tid < 16) reinterpret_cast<uint32_t*>(smem + L.zero(K))[tid] = 0;
     if (tid == 0) *xmax = 0;
+    peer_wait_previous(pp, tid, status);
     __syncthreads();
     const uint4* xg = reinterpret_cast<const uint4*>(x);
     uint4* xv = reinterpret_cast<uint4*>(smem + L.x);
@@ -351,7 +353,7 @@ gemv_q6k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
       for (int jj = 0; jj < 8; jj++) v += redbuf[((r >> 4) * 8 + jj) * 16 + (r & 15)];
       const int row = rg * kRowsPerUnit + r;
       if (complete) {
-        if (row < N) store_out(y, y_dtype, row, v);
+        if (row < N) peer_emit(pp, y, y_dtype, row, v);
       } else {
         const int slot_p = (rg == rg_begin) ? 0 : 1;
         float* mine = partials + ((int64_t)b * 2 + slot_p) * 64;
@@ -369,7 +371,7 @@ gemv_q6k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
             const int sl = (rg == (int)((U * bb / G) / C)) ? 0 : 1;
             s0 += __ldcg(partials + ((int64_t)bb * 2 + sl) * 64 + lane);
           }
-          if (row < N) store_out(y, y_dtype, row, s0);
+          if (row < N) peer_emit(pp, y, y_dtype, row, s0);
           if (lane == 0) counters[rg] = 0;
         }
       }
@@ -377,6 +379,7 @@ gemv_q6k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
     if (c == C) { c = 0; ++rg; }
   }
   cp_async_wait<0>();
+  peer_publish(pp, tid, G);
 }
 
 }  // namespace q6k
@@ -387,8 +390,10 @@ bool gemv_q6k_applicable(int64_t N, int64_t K, int M, const void* w, const void*
 }
 
 cudaError_t gemv_q6k(const uint8_t* w, int64_t N, int64_t K, const void* x, void* y, int y_dtype, void* ws,
-                     size_t ws_bytes, int sm_count, cudaStream_t st) {
+                     size_t ws_bytes, int sm_count, int* status, cudaStream_t st, const PeerPublish* peers) {
   using namespace q6k;
+  PeerPublish pp = {};
+  if (peers) pp = *peers;
   if (ws_bytes < gemv_q4k_workspace_bytes(N, sm_count) || !ws || sm_count > kMaxSmCount) return cudaErrorInvalidValue;
   const int64_t RG = (N + kRowsPerUnit - 1) / kRowsPerUnit;
   const int64_t U = RG * (K / 256 / kSbPerUnit);
@@ -410,9 +415,9 @@ cudaError_t gemv_q6k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
   float* partials = reinterpret_cast<float*>(ws);
   int* counters = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ws) + kWsCounterOffset);
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
-  if (depth == 4) gemv_q6k_m1_kernel<4><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
-  else if (depth == 3) gemv_q6k_m1_kernel<3><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
-  else gemv_q6k_m1_kernel<2><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials);
+  if (depth == 4) gemv_q6k_m1_kernel<4><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
+  else if (depth == 3) gemv_q6k_m1_kernel<3><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
+  else gemv_q6k_m1_kernel<2><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
   return cudaPeekAtLastError();
 }
 

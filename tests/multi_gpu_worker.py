@@ -47,10 +47,10 @@ def main():
         same(y, single, f"rank {rank}: all-gather route ({qt.name})")
         ref = O.c_matmul(O.bf16_bits(xb), wb, qt)
         assert O.rel_l2(y.float().cpu().numpy(), ref) <= 2e-3
-    # fused peer-store exchange (Q4_K, batch 1): three chained launches reuse both buffers
-    qt, m = QT.Q4_K, 1
+    # fused peer-store exchange (batch 1): chained launches of the three tuned kernels reuse both buffers
+    m = 1
     out = sharded.PeerOutput(None, max_batch=1, n_total=n, device=dev)
-    for step in range(3):
+    for step, qt in enumerate((QT.Q4_K, QT.Q6_K, QT.Q5_K, QT.Q4_K, QT.Q6_K)):
         wb = synth.make_weight_bytes(n, k, qt, seed=20 + step)
         xb = synth.make_x(m, k, seed=30 + step)
         w = gj.QuantizedArray.from_bytes(wb, qt, shape=(n, k), device=dev)
