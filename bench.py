@@ -8,8 +8,9 @@ total size is a multiple of the 126 MB L2, so every step streams its weight from
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 N > 1 (launched under torchrun, one rank per GPU): the weight's output rows are sharded
-across the ranks, every rank multiplies its slice and an NCCL all-gather rebuilds the
-replicated ``y`` -- total work is fixed, so scaling is "strong".
+across the ranks, every rank multiplies its slice and the kernel's epilogue stores the rows
+into every rank's output over NVLink (NCCL all-gather if symmetric memory is unavailable)
+-- total work is fixed, so scaling is "strong".
 
 Rank 0 prints ONE JSON line.  Keys beyond the common contract:
   roofline     achieved = algorithmic bytes of one launch / mean launch time (CUDA events
@@ -17,6 +18,12 @@ Rank 0 prints ONE JSON line.  Keys beyond the common contract:
                bandwidth from MEASURED_PEAKS.json (fallback 6650 GB/s, marked as such).
   cpu_baseline the CPU restatement of the same multiply (oracle/, OpenMP) timed on this
                host on a bounded row sample of the same weight.
+  decode       tokens/s of a Llama-3-70B-shaped Q4_K_M decode step at batch 1 (the second half
+               of the headline metric): per layer five fused GEMVs -- q+k (Q4_K 9216x8192),
+               v (Q6_K 1024x8192), o (Q4_K 8192x8192), gate+up (Q4_K 57344x8192), down (Q6_K
+               8192x28672) -- 80 layers, then the Q6_K lm_head 128256x8192; every GEMV is
+               row-sharded over the N ranks.  Norms, RoPE, attention and sampling are outside the
+               reference and are not run: each GEMV reads a fixed synthetic activation vector.
   e2e          the same multiply through the public API (gguf_jax_b200.matmul) with the
                activation coming from pinned host memory and the result read back to the
                host inside the timed region; the weight stays resident on the device, as in
@@ -143,6 +150,91 @@ def cpu_baseline(seconds: float = 10.0, rows: int = 1024) -> dict:
                       f"(K={K_DIM}, batch {BATCH}) in {dt:.1f} s; fused decode+dot, float32, OpenMP"}
 
 
+# Llama-3-70B-shaped Q4_K_M decode step: (name, qtype, rows, K) of the fused GEMVs of one layer.
+DECODE_LAYER = [("qk", "Q4_K", 9216, 8192), ("v", "Q6_K", 1024, 8192), ("o", "Q4_K", 8192, 8192),
+                ("gate_up", "Q4_K", 57344, 8192), ("down", "Q6_K", 8192, 28672)]
+DECODE_HEAD = ("lm_head", "Q6_K", 128256, 8192)
+DECODE_LAYERS = 80
+DECODE_DISTINCT = 8      # distinct layer weight sets cycled through the 80 layer steps
+_BLOCK_BYTES = {"Q4_K": 144, "Q6_K": 210}
+
+
+def decode_leg(world: int, rank: int, dev, peer_factory) -> dict:
+    """Time one decode step (batch 1) of the 70B-shaped model; see the module docstring."""
+    import torch
+    import torch.distributed as dist
+    from gguf.constants import GGMLQuantizationType as QT
+
+    import gguf_jax_b200 as gj
+    from gguf_jax_b200 import kernels, synth
+
+    def shard(qt_name, rows, k, seed):
+        qt = QT[qt_name]
+        rows_local = rows // world
+        assert rows_local * world == rows
+        # only this rank's rows are ever generated (row-sliced upload)
+        w = synth.make_weight_on_device(rows_local, k, qt, seed=seed * 64 + rank, device=dev)
+        return gj.QuantizedArray(w.data, qt, (rows_local, k))
+
+    layers = [[shard(q, n, k, 100 + 10 * li + i) for i, (_, q, n, k) in enumerate(DECODE_LAYER)]
+              for li in range(DECODE_DISTINCT)]
+    head = shard(DECODE_HEAD[1], DECODE_HEAD[2], DECODE_HEAD[3], 999)
+    xs = {k: torch.from_numpy(synth.make_x(1, k, seed=k)).to(dev).to(torch.bfloat16) for k in (8192, 28672)}
+    peer = peer_factory(DECODE_HEAD[2]) if world > 1 else None
+
+    def gemv(w):
+        x = xs[w.shape[1]]
+        if peer is not None:
+            return peer.matmul(x, w, wait_previous=True)
+        return kernels.fused_matmul(x, w)
+
+    def token():
+        for li in range(DECODE_LAYERS):
+            for w in layers[li % DECODE_DISTINCT]:
+                gemv(w)
+        return gemv(head)
+
+    stream = torch.cuda.Stream(dev)
+    with torch.cuda.stream(stream):
+        token()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            token()
+    torch.cuda.synchronize()
+
+    def one() -> float:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    for _ in range(3):
+        one()
+    ms = statistics.median([one() for _ in range(10)])
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    launches = DECODE_LAYERS * len(DECODE_LAYER) + 1
+    wbytes = sum(n * (k // 256) * _BLOCK_BYTES[q] for _, q, n, k in DECODE_LAYER) * DECODE_LAYERS
+    wbytes += DECODE_HEAD[2] * (DECODE_HEAD[3] // 256) * _BLOCK_BYTES[DECODE_HEAD[1]]
+    del graph
+    return {"tok_s": 1e3 / ms, "ms_per_token": ms, "batch": 1, "launches_per_token": launches,
+            "weight_gb_per_token": wbytes / 1e9, "aggregate_hbm_gbs": wbytes / (ms * 1e-3) / 1e9,
+            "model": "Llama-3-70B-shaped Q4_K_M (attn_v, ffn_down, lm_head in Q6_K), GEMVs only",
+            "note": f"{DECODE_LAYERS} layer steps cycle over {DECODE_DISTINCT} distinct synthetic layer weight sets "
+                    "(each far larger than L2); fixed synthetic activations between GEMVs; one CUDA graph per token"}
+
+
 def run_reference(args) -> None:
     """--impl reference: the CPU route on this host's cores; rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
@@ -195,7 +287,7 @@ def run_ours(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     _lib.lib()
-    qt = QT[QTYPE_NAME]
+    qt = QT[args.profile_qtype if args.profile else QTYPE_NAME]
 
     rows_local = N_ROWS // world
     assert rows_local * world == N_ROWS
@@ -346,6 +438,17 @@ def run_ours(args) -> None:
         e2e_s = float(t.item())
     e2e_value = algorithmic_bytes(N_ROWS, K_DIM, BATCH) * e2e_steps / e2e_s / 1e9
 
+    decode = None
+    if not args.no_decode:
+        # free the headline weights first: the decode leg brings its own
+        weights.clear()
+        torch.cuda.empty_cache()
+        try:
+            decode = decode_leg(world, rank, dev,
+                                lambda n: sharded.PeerOutput(None, max_batch=1, n_total=n, device=dev))
+        except Exception as e:  # noqa: BLE001
+            decode = {"unavailable": f"{type(e).__name__}: {e}"}
+
     if rank == 0:
         cpu = cpu_baseline() if world == 1 else None
         line = {
@@ -374,6 +477,8 @@ def run_ours(args) -> None:
                     "note": "weight resident on the device; activation H2D from pinned memory and result D2H every step"},
             "gpu_launches": args.steps * launches_per_step,
         }
+        if decode is not None:
+            line["decode"] = decode
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line))
@@ -395,6 +500,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-qtype", default=QTYPE_NAME, choices=["Q4_K", "Q5_K", "Q6_K"],
+                    help="with --profile: the qtype of the 8192x28672 weight (each has its own tuned kernel)")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode-step (tokens/s) leg")
     ap.add_argument("--profile", action="store_true",
                     help="profiler-friendly run: a few eager launches of the hot kernel, no graph, "
                          "no CPU baseline, no end-to-end leg, no JSON line")

@@ -40,6 +40,30 @@ struct PeerPublish {
 };
 
 #ifdef __CUDACC__
+// Programmatic dependent launch.  The batch-1 kernels are launched with the stream-serialization
+// attribute: the next kernel of the stream may start while this one drains, stream its first
+// weight tiles (which no kernel writes) into shared memory, and block in pdl_wait() until the
+// previous kernel has completed and its memory is visible -- before it touches activations,
+// scratch or outputs.  pdl_trigger() at the top of a kernel lets its own successor do the same.
+// Both are no-ops when the launch did not carry the attribute.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Consumer side, threads tid < world of one CTA (every CTA does it): the activations were produced
 // by the previous exchange, whose number is this rank's own epoch; wait until every rank has
 // raised its flag here to that number.  Bounded (about 50 ms of wall time); when it runs out the

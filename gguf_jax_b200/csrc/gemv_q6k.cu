@@ -171,6 +171,7 @@ gemv_q6k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
                    void* __restrict__ y, int y_dtype, int* __restrict__ counters, float* __restrict__ partials,
                    const PeerPublish pp, int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int SB = K / 256;                        // superblocks per row (a multiple of 8)
   const int row_bytes = SB * kBlockBytes;        // a multiple of 16
@@ -238,6 +239,7 @@ gemv_q6k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
   {
     if (tid < 16) reinterpret_cast<uint32_t*>(smem + L.zero(K))[tid] = 0;
     if (tid == 0) *xmax = 0;
+    pdl_wait();   // everything below reads or writes memory that the previous kernel may still be using
     peer_wait_previous(pp, tid, status);
     __syncthreads();
     const uint4* xg = reinterpret_cast<const uint4*>(x);
@@ -415,10 +417,11 @@ cudaError_t gemv_q6k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
   float* partials = reinterpret_cast<float*>(ws);
   int* counters = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ws) + kWsCounterOffset);
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
-  if (depth == 4) gemv_q6k_m1_kernel<4><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
-  else if (depth == 3) gemv_q6k_m1_kernel<3><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
-  else gemv_q6k_m1_kernel<2><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
-  return cudaPeekAtLastError();
+  cudaError_t err;
+  if (depth == 4) err = launch_pdl(gemv_q6k_m1_kernel<4>, grid, kThreads, smem, st, w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
+  else if (depth == 3) err = launch_pdl(gemv_q6k_m1_kernel<3>, grid, kThreads, smem, st, w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
+  else err = launch_pdl(gemv_q6k_m1_kernel<2>, grid, kThreads, smem, st, w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
+  return err != cudaSuccess ? err : cudaPeekAtLastError();
 }
 
 }  // namespace ggq

@@ -116,8 +116,9 @@ class PeerOutput:
         that on the device; host code must synchronise and pass a barrier before reading it)."""
         if len(w_shard.shape) != 2 or x.shape[-1] != w_shard.shape[1]:
             raise ValueError(f"contraction mismatch: x {tuple(x.shape)}, w {w_shard.shape}")
-        if w_shard.shape[0] * self.world != self.n_total:
-            raise ValueError(f"{self.world} shards of {w_shard.shape[0]} rows do not make {self.n_total}")
+        n_out = w_shard.shape[0] * self.world
+        if n_out > self.n_total:
+            raise ValueError(f"{self.world} shards of {w_shard.shape[0]} rows exceed the buffers' {self.n_total} columns")
         k = w_shard.shape[1]
         xm = x.reshape(-1, k).contiguous()
         m = xm.shape[0]
@@ -132,8 +133,9 @@ class PeerOutput:
             ws = _backend.workspace(dev, L.ggq_workspace_bytes(int(w_shard.qtype), w_shard.shape[0], k, m))
             _lib.check(L.ggq_gemv_sharded(
                 int(w_shard.qtype), w_shard.data.data_ptr(), w_shard.shape[0], k, xm.data_ptr(), m,
-                self._buf_ptrs[turn], self._flag_ptrs, self.world, self.rank, self.n_total,
+                self._buf_ptrs[turn], self._flag_ptrs, self.world, self.rank, n_out,
                 _backend.dtype_code(self.dtype), 1 if wait_previous else 0,
                 ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
                 _backend.stream_ptr(dev)))
-        return self._bufs[turn][:m]
+        # a narrower product uses the front of the buffer as a dense (m, n_out) array
+        return self._bufs[turn].view(-1)[: m * n_out].view(m, n_out)
