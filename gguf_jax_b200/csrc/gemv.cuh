@@ -99,20 +99,22 @@ __device__ __forceinline__ void peer_emit(const PeerPublish& pp, void* y, int y_
 }
 // Producer side, called by every thread of every CTA at the end of the kernel: once every CTA of
 // the launch has pushed its rows to the peers, raise this rank's flag everywhere.
-// fence -> counter -> (last CTA) fence -> flag stores orders all the data stores of the grid
-// before the flag as seen from any GPU.
+// Ordering: a CTA's peer stores -> bar.sync -> fence (GPU scope) -> counter; the last CTA reads the
+// counter, fences at system scope and releases the flags.  Causality is transitive across the two
+// scopes, so a peer that acquires the flag sees every CTA's stores; only one thread of the grid
+// pays for a system-scope fence (148 of them at the tail of a 30 us kernel were measurable).
 __device__ __forceinline__ void peer_publish(const PeerPublish& pp, int tid, int n_ctas) {
   if (pp.world > 0) {
     __syncthreads();
     if (tid == 0) {
       uint32_t* mine = pp.flags[pp.rank];
-      __threadfence_system();
+      __threadfence();
       const uint32_t done = atomicAdd(mine + pp.world + 1, 1u);
       if (done == (uint32_t)n_ctas - 1) {
+        __threadfence_system();
         mine[pp.world + 1] = 0;
         const uint32_t epoch = mine[pp.world] + 1;
         mine[pp.world] = epoch;
-        __threadfence_system();
         for (int p = 0; p < pp.world; p++)
           asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pp.flags[p] + pp.rank), "r"(epoch) : "memory");
       }
