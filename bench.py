@@ -159,14 +159,31 @@ DECODE_DISTINCT = 8      # distinct layer weight sets cycled through the 80 laye
 _BLOCK_BYTES = {"Q4_K": 144, "Q6_K": 210}
 
 
-def decode_leg(world: int, rank: int, dev, peer_factory) -> dict:
-    """Time one decode step (batch 1) of the 70B-shaped model; see the module docstring."""
+def _scale_block_scales(w, log2: int) -> None:
+    """Multiply the float16 super-block scales of a Q4_K / Q6_K payload by 2^log2 in place (exact)."""
+    import torch
+    ts = _BLOCK_BYTES[w.qtype.name]
+    blocks = w.data.view(-1, ts)
+    cols = slice(0, 4) if w.qtype.name == "Q4_K" else slice(208, 210)
+    f = blocks[:, cols].contiguous().view(torch.float16)
+    blocks[:, cols] = (f.float() * (2.0 ** log2)).to(torch.float16).view(torch.uint8)
+
+
+def decode_leg(world: int, rank: int, dev) -> dict:
+    """Time one decode step (batch 1) of the 70B-shaped model; see the module docstring.
+
+    The GEMVs are chained for real: q+k and v read the previous layer's down output, o reads the
+    first 8192 outputs of q+k, gate+up reads o, down reads the first 28672 outputs of gate+up, the
+    lm_head reads the last down output.  (Attention, norms and activations are not run, so the
+    numbers mean nothing; the block scales are shifted by powers of two beforehand so that the
+    magnitudes stay near one along the chain.)  On N > 1 ranks every product is row-sharded and
+    its result reaches every rank through the tagged exchange inside the kernels."""
     import torch
     import torch.distributed as dist
     from gguf.constants import GGMLQuantizationType as QT
 
     import gguf_jax_b200 as gj
-    from gguf_jax_b200 import kernels, synth
+    from gguf_jax_b200 import kernels, sharded, synth
 
     def shard(qt_name, rows, k, seed):
         qt = QT[qt_name]
@@ -179,28 +196,65 @@ def decode_leg(world: int, rank: int, dev, peer_factory) -> dict:
     layers = [[shard(q, n, k, 100 + 10 * li + i) for i, (_, q, n, k) in enumerate(DECODE_LAYER)]
               for li in range(DECODE_DISTINCT)]
     head = shard(DECODE_HEAD[1], DECODE_HEAD[2], DECODE_HEAD[3], 999)
-    xs = {k: torch.from_numpy(synth.make_x(1, k, seed=k)).to(dev).to(torch.bfloat16) for k in (8192, 28672)}
-    peer = peer_factory(DECODE_HEAD[2]) if world > 1 else None
+    launches = DECODE_LAYERS * len(DECODE_LAYER) + 1
+    x0 = torch.from_numpy(synth.make_x(1, 8192, seed=8192)).to(dev).to(torch.bfloat16)
 
-    def gemv(w):
-        x = xs[w.shape[1]]
-        if peer is not None:
-            return peer.matmul(x, w, wait_previous=True)
-        return kernels.fused_matmul(x, w)
+    if world > 1:
+        ex = sharded.TaggedExchange(None, n_max=DECODE_HEAD[2], device=dev,
+                                    n_buffers=sharded.TaggedExchange.buffers_for(launches, max_back=2))
+
+        def mm(x, w):
+            return ex.matmul(x, w)
+
+        def value(h):
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            return h.to_tensor().clone()
+    else:
+        def mm(x, w):
+            return kernels.fused_matmul(x[:, :w.shape[1]], w)
+
+        def value(h):
+            return h
+
+    def layer_step(h, ws):
+        qk = mm(h, ws[0])
+        mm(h, ws[1])                 # v: consumed by attention, which is not run
+        o = mm(qk, ws[2])
+        gu = mm(o, ws[3])
+        return mm(gu, ws[4])
+
+    # calibration: shift every matrix's block scales so that its output has rms ~ 1 for an rms ~ 1 input
+    def calibrate(x, w):
+        y = value(mm(x, w)).float()
+        rms = float(y.pow(2).mean().sqrt())
+        sh = -int(round(__import__("math").log2(rms))) if rms > 0 and rms == rms else 0
+        _scale_block_scales(w, sh)
+        return (y * 2.0 ** sh).to(torch.bfloat16)
+
+    h = x0
+    for ws in layers:
+        qk = calibrate(h, ws[0])
+        calibrate(h, ws[1])
+        o = calibrate(qk[:, :8192].contiguous(), ws[2])
+        gu = calibrate(o, ws[3])
+        h = calibrate(gu[:, :28672].contiguous(), ws[4])
+    calibrate(h, head)
 
     def token():
+        h = x0
         for li in range(DECODE_LAYERS):
-            for w in layers[li % DECODE_DISTINCT]:
-                gemv(w)
-        return gemv(head)
+            h = layer_step(h, layers[li % DECODE_DISTINCT])
+        return mm(h, head)
 
     stream = torch.cuda.Stream(dev)
     with torch.cuda.stream(stream):
-        token()
+        logits = token()
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            token()
+            logits = token()
     torch.cuda.synchronize()
 
     def one() -> float:
@@ -224,15 +278,24 @@ def decode_leg(world: int, rank: int, dev, peer_factory) -> dict:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    launches = DECODE_LAYERS * len(DECODE_LAYER) + 1
+    lv = value(logits).float()
+    finite = bool(torch.isfinite(lv).all())
     wbytes = sum(n * (k // 256) * _BLOCK_BYTES[q] for _, q, n, k in DECODE_LAYER) * DECODE_LAYERS
     wbytes += DECODE_HEAD[2] * (DECODE_HEAD[3] // 256) * _BLOCK_BYTES[DECODE_HEAD[1]]
+    import ctypes
+
+    from gguf_jax_b200 import _lib
+    word = ctypes.c_int32(0)
+    _lib.lib().ggq_read_status(dev.index, ctypes.byref(word))
     del graph
     return {"tok_s": 1e3 / ms, "ms_per_token": ms, "batch": 1, "launches_per_token": launches,
             "weight_gb_per_token": wbytes / 1e9, "aggregate_hbm_gbs": wbytes / (ms * 1e-3) / 1e9,
-            "model": "Llama-3-70B-shaped Q4_K_M (attn_v, ffn_down, lm_head in Q6_K), GEMVs only",
+            "logits_finite": finite, "logits_rms": float(lv.pow(2).mean().sqrt()), "device_status": int(word.value),
+            "exchange": "tagged words stored into every rank's buffer by the kernels (ggq_gemv_sharded_tagged)" if world > 1 else "none",
+            "model": "Llama-3-70B-shaped Q4_K_M (attn_v, ffn_down, lm_head in Q6_K), GEMVs only, chained",
             "note": f"{DECODE_LAYERS} layer steps cycle over {DECODE_DISTINCT} distinct synthetic layer weight sets "
-                    "(each far larger than L2); fixed synthetic activations between GEMVs; one CUDA graph per token"}
+                    "(each far larger than L2); block scales shifted by powers of two so the chain stays near unit "
+                    "magnitude; one CUDA graph per token"}
 
 
 def run_reference(args) -> None:
@@ -444,8 +507,7 @@ def run_ours(args) -> None:
         weights.clear()
         torch.cuda.empty_cache()
         try:
-            decode = decode_leg(world, rank, dev,
-                                lambda n: sharded.PeerOutput(None, max_batch=1, n_total=n, device=dev))
+            decode = decode_leg(world, rank, dev)
         except Exception as e:  # noqa: BLE001
             decode = {"unavailable": f"{type(e).__name__}: {e}"}
 

@@ -133,6 +133,54 @@ extern "C" int32_t ggq_gemv_sharded(int32_t qtype, const void* w, int64_t N_loca
   return GGQ_OK;
 }
 
+extern "C" int32_t ggq_gemv_sharded_tagged(int32_t qtype, const void* w, int64_t N_local, int64_t K,
+                                           const void* x_bf16, const uint32_t* x_tagged, int32_t x_back,
+                                           uint32_t* const* y_peers, uint32_t* state, int32_t world, int32_t rank,
+                                           int64_t n_total, void* workspace, size_t workspace_bytes, void* stream) {
+  const TypeInfo* ti = type_info(qtype);
+  if (!ti) return fail(GGQ_BAD_QTYPE, "ggq_gemv_sharded_tagged: qtype %d is not decodable", qtype);
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+    return fail(GGQ_BAD_SHAPE, "ggq_gemv_sharded_tagged: rank %d of %d (at most %d ranks)", rank, world, kMaxPeers);
+  if (N_local <= 0 || K <= 0 || K % ti->block_elems || n_total < (int64_t)world * N_local)
+    return fail(GGQ_BAD_SHAPE, "ggq_gemv_sharded_tagged: N_local=%lld K=%lld n_total=%lld", (long long)N_local,
+                (long long)K, (long long)n_total);
+  if (!w || !y_peers || !state || (!x_bf16) == (!x_tagged))
+    return fail(GGQ_MISALIGNED, "ggq_gemv_sharded_tagged: null pointer (give exactly one of x_bf16, x_tagged)");
+  if (x_tagged && (x_back < 1 || x_back > 65534))
+    return fail(GGQ_BAD_SHAPE, "ggq_gemv_sharded_tagged: x_back=%d", x_back);
+  const void* xa = x_bf16 ? x_bf16 : (const void*)x_tagged;
+  const bool ok4 = qtype == QT_Q4_K && gemv_q4k_applicable(N_local, K, 1, w, xa);
+  const bool ok5 = qtype == QT_Q5_K && gemv_q5k_applicable(N_local, K, 1, w, xa);
+  const bool ok6 = qtype == QT_Q6_K && gemv_q6k_applicable(N_local, K, 1, w, xa);
+  if (!(ok4 || ok5 || ok6))
+    return fail(GGQ_UNSUPPORTED, "ggq_gemv_sharded_tagged: only the Q4_K / Q5_K / Q6_K batch-1 kernels take part in "
+                "the tagged exchange (qtype %d, K=%lld)", qtype, (long long)K);
+  if (!workspace || workspace_bytes < gemv_q4k_workspace_bytes(N_local, kMaxSmCount) || (uintptr_t)workspace % 256)
+    return fail(GGQ_BAD_WORKSPACE, "ggq_gemv_sharded_tagged: workspace of %zu bytes needed",
+                gemv_q4k_workspace_bytes(N_local, kMaxSmCount));
+  int dev = 0;
+  cudaGetDevice(&dev);
+  PeerPublish pp = {};
+  for (int p = 0; p < world; p++) {
+    if (!y_peers[p]) return fail(GGQ_MISALIGNED, "ggq_gemv_sharded_tagged: null peer pointer %d", p);
+    pp.y[p] = y_peers[p];
+  }
+  pp.flags[rank] = state;
+  pp.world = world;
+  pp.rank = rank;
+  pp.n_total = n_total;
+  pp.row_offset = (int64_t)rank * N_local;
+  pp.tagged = 1;
+  pp.x_tagged = x_tagged;
+  pp.x_back = x_tagged ? x_back : 1;
+  cudaError_t (*kernel)(const uint8_t*, int64_t, int64_t, const void*, void*, int, void*, size_t, int, int*,
+                        cudaStream_t, const PeerPublish*) = ok4 ? gemv_q4k : ok5 ? gemv_q5k : gemv_q6k;
+  cudaError_t err = kernel((const uint8_t*)w, N_local, K, xa, nullptr, GGQ_BF16, workspace, workspace_bytes,
+                           sm_count_of(dev), device_status_word(dev), (cudaStream_t)stream, &pp);
+  if (err != cudaSuccess) return fail(GGQ_LAUNCH_FAILED, "ggq_gemv_sharded_tagged: %s", cudaGetErrorString(err));
+  return GGQ_OK;
+}
+
 extern "C" int32_t ggq_gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x_bf16, void* y,
                                        int32_t y_dtype, void* stream) {
   if (y_dtype != GGQ_F32 && y_dtype != GGQ_BF16 && y_dtype != GGQ_F16)

@@ -32,12 +32,22 @@ struct PeerPublish {
   int64_t n_total;                // row stride of the full output
   int64_t row_offset;             // first output row of this rank's slice
   int wait_previous;              // 1: the activations come from the previous exchange, wait for it first
+  // Tagged mode (no flags, no fences): every output element travels as one 32-bit word, bf16 value
+  // in the low half and the exchange's 16-bit tag in the high half, so a word validates itself and
+  // the only cost of the exchange is the flight time of the stores.  y[] are then uint32 buffers;
+  // a consumer kernel given x_tagged polls each word until its tag is the expected one (bounded).
+  int tagged;                     // 1: emit tagged words, do not raise flags
+  const uint32_t* x_tagged;       // activations as tagged words of an earlier exchange (nullptr: plain bf16 x)
+  int x_back;                     // that exchange was the x_back-th most recent one (1 = the previous launch)
   // Each flag array has world + 2 words: [0, world) are raised by the peers; word `world` is this
   // rank's epoch (number of exchanges it has published), word world + 1 counts finished CTAs of
   // the running launch.  All ranks issue the same sequence of sharded launches, so "the previous
   // exchange" is the one whose number equals this rank's own epoch: no host-side sequence
-  // numbers, and a captured CUDA graph can be replayed.
+  // numbers, and a captured CUDA graph can be replayed.  Tags are derived from the same epoch.
 };
+
+// Tag of exchange number e (1-based): 1..65535, never 0 (a zero-filled buffer is invalid).
+__host__ __device__ inline uint32_t peer_tag_of(uint32_t e) { return e % 65535u + 1u; }
 
 #ifdef __CUDACC__
 // Programmatic dependent launch.  The batch-1 kernels are launched with the stream-serialization
@@ -89,10 +99,42 @@ __device__ __forceinline__ void peer_wait_previous(const PeerPublish& pp, int ti
     if (!ok && status) atomicOr(status, STATUS_WAIT_EXPIRED);
   }
 }
+// Eight consecutive activations (as raw bf16 pairs, the layout of a plain uint4 load) from a tagged
+// vector: two 16-byte loads of tagged words, repeated until all eight tags match (bounded: about
+// 50 ms, then the status word is raised and whatever is there is used).
+__device__ __forceinline__ uint4 peer_load8_tagged(const uint32_t* xt, int idx8, uint32_t tag_hi, int* status) {
+  const uint32_t* p = xt + 8 * (int64_t)idx8;
+  uint4 a, b;
+  uint64_t t0 = 0;
+  for (uint32_t i = 0;; i++) {
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(p) : "memory");
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p + 4) : "memory");
+    const uint32_t bad = ((a.x ^ tag_hi) | (a.y ^ tag_hi) | (a.z ^ tag_hi) | (a.w ^ tag_hi) |
+                          (b.x ^ tag_hi) | (b.y ^ tag_hi) | (b.z ^ tag_hi) | (b.w ^ tag_hi)) >> 16;
+    if (!bad) break;
+    if ((i & 63) == 0) {
+      uint64_t t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (i == 0) t0 = t1;
+      else if (t1 - t0 > 50000000ull) { if (status) atomicOr(status, STATUS_WAIT_EXPIRED); break; }
+    }
+  }
+  // word pairs (lo16 of even element | lo16 of odd element << 16)
+  return make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410),
+                    __byte_perm(b.x, b.y, 0x5410), __byte_perm(b.z, b.w, 0x5410));
+}
+
 // One output value: locally, or into every rank's copy of the full output when row-sharded.
-__device__ __forceinline__ void peer_emit(const PeerPublish& pp, void* y, int y_dtype, int64_t row, float v) {
+// out_tag: the running exchange's tag, already shifted into the high half (tagged mode only).
+__device__ __forceinline__ void peer_emit(const PeerPublish& pp, void* y, int y_dtype, int64_t row, float v,
+                                          uint32_t out_tag = 0) {
   if (pp.world == 0) {
     store_out(y, y_dtype, row, v);
+  } else if (pp.tagged) {
+    const uint32_t word = out_tag | (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+    for (int p = 0; p < pp.world; p++)
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t*>(pp.y[p]) + pp.row_offset + row),
+                   "r"(word) : "memory");
   } else {
     for (int p = 0; p < pp.world; p++) store_out(pp.y[p], y_dtype, pp.row_offset + row, v);
   }
@@ -104,7 +146,18 @@ __device__ __forceinline__ void peer_emit(const PeerPublish& pp, void* y, int y_
 // scopes, so a peer that acquires the flag sees every CTA's stores; only one thread of the grid
 // pays for a system-scope fence (148 of them at the tail of a 30 us kernel were measurable).
 __device__ __forceinline__ void peer_publish(const PeerPublish& pp, int tid, int n_ctas) {
-  if (pp.world > 0) {
+  if (pp.world > 0 && pp.tagged) {
+    // tagged mode: nothing to tell the peers; the last CTA advances this rank's own epoch
+    __syncthreads();
+    if (tid == 0) {
+      uint32_t* mine = pp.flags[pp.rank];
+      const uint32_t done = atomicAdd(mine + pp.world + 1, 1u);
+      if (done == (uint32_t)n_ctas - 1) {
+        mine[pp.world + 1] = 0;
+        mine[pp.world] = mine[pp.world] + 1;
+      }
+    }
+  } else if (pp.world > 0) {
     __syncthreads();
     if (tid == 0) {
       uint32_t* mine = pp.flags[pp.rank];

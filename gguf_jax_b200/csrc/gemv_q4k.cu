@@ -259,6 +259,7 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
 
   float* xs = reinterpret_cast<float*>(smem + L.xs(K));
   int* xmax = reinterpret_cast<int*>(smem + L.misc(K));
+  uint32_t out_tag = 0, x_tag = 0;   // tagged exchange: this launch's tag and the tag its activations carry
   int S;  // activations are held as x * 2^S (even sub-blocks) / x * 2^(S-4) (odd sub-blocks)
   {
     // Once per CTA: zero page, per-sub-block sums X, largest |x|, then x written to shared
@@ -267,6 +268,11 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
     if (tid == 0) *xmax = 0;
     pdl_wait();   // everything below reads or writes memory that the previous kernel may still be using
     peer_wait_previous(pp, tid, status);
+    if (pp.world > 0 && pp.tagged) {
+      const uint32_t e = pp.flags[pp.rank][pp.world];        // exchanges this rank has completed
+      out_tag = peer_tag_of(e + 1) << 16;
+      x_tag = peer_tag_of(e + 1 - (uint32_t)pp.x_back) << 16;
+    }
     __syncthreads();
     const uint4* xg = reinterpret_cast<const uint4*>(x);
     uint4* xv = reinterpret_cast<uint4*>(smem + L.x);
@@ -287,7 +293,8 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
         const float up = (sblk & 1) ? up_odd : up_even;
         uint4 v[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) v[q] = __ldg(xg + sblk * 4 + q);
+        for (int q = 0; q < 4; q++)
+          v[q] = pp.x_tagged ? peer_load8_tagged(pp.x_tagged, sblk * 4 + q, x_tag, status) : __ldg(xg + sblk * 4 + q);
         float sum = 0.f, asum = 0.f;
 #pragma unroll
         for (int q = 0; q < 4; q++) {
@@ -332,7 +339,7 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
   const LaneScale lc(t);
   float* red = reinterpret_cast<float*>(smem + L.red(K));
 
-  auto emit = [&](int row, float v) { peer_emit(pp, y, y_dtype, row, v); };
+  auto emit = [&](int row, float v) { peer_emit(pp, y, y_dtype, row, v, out_tag); };
 
   // ---- multiply side: walk my units row group by row group ----
   int rg = rg_begin, c = c_begin, done = 0, slot = 0, flush_parity = 0;

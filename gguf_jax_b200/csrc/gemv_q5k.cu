@@ -209,12 +209,18 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
 
   float* xs = reinterpret_cast<float*>(smem + L.xs(K));
   int* xmax = reinterpret_cast<int*>(smem + L.misc(K));
+  uint32_t out_tag = 0, x_tag = 0;   // tagged exchange: this launch's tag and the tag its activations carry
   int S;  // activations are held as x * 2^S (even sub-blocks) / x * 2^(S-4) (odd sub-blocks)
   {
     if (tid < 16) reinterpret_cast<uint32_t*>(smem + L.zero(K))[tid] = 0;
     if (tid == 0) *xmax = 0;
     pdl_wait();   // everything below reads or writes memory that the previous kernel may still be using
     peer_wait_previous(pp, tid, status);
+    if (pp.world > 0 && pp.tagged) {
+      const uint32_t e = pp.flags[pp.rank][pp.world];        // exchanges this rank has completed
+      out_tag = peer_tag_of(e + 1) << 16;
+      x_tag = peer_tag_of(e + 1 - (uint32_t)pp.x_back) << 16;
+    }
     __syncthreads();
     const uint4* xg = reinterpret_cast<const uint4*>(x);
     uint4* xv = reinterpret_cast<uint4*>(smem + L.x);
@@ -233,7 +239,8 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
         const float up = (sblk & 1) ? up_odd : up_even;
         uint4 v[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) v[q] = __ldg(xg + sblk * 4 + q);
+        for (int q = 0; q < 4; q++)
+          v[q] = pp.x_tagged ? peer_load8_tagged(pp.x_tagged, sblk * 4 + q, x_tag, status) : __ldg(xg + sblk * 4 + q);
         float sum = 0.f, asum = 0.f;
 #pragma unroll
         for (int q = 0; q < 4; q++) {
@@ -318,7 +325,7 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
       for (int jj = 0; jj < 8; jj++) v += redbuf[((r >> 4) * 8 + jj) * 16 + (r & 15)];
       const int row = rg * kRowsPerUnit + r;
       if (complete) {
-        if (row < N) peer_emit(pp, y, y_dtype, row, v);
+        if (row < N) peer_emit(pp, y, y_dtype, row, v, out_tag);
       } else {
         const int slot_p = (rg == rg_begin) ? 0 : 1;
         float* mine = partials + ((int64_t)b * 2 + slot_p) * 64;
@@ -336,7 +343,7 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
             const int sl = (rg == (int)((U * bb / G) / C)) ? 0 : 1;
             s0 += __ldcg(partials + ((int64_t)bb * 2 + sl) * 64 + lane);
           }
-          if (row < N) peer_emit(pp, y, y_dtype, row, s0);
+          if (row < N) peer_emit(pp, y, y_dtype, row, s0, out_tag);
           if (lane == 0) counters[rg] = 0;
         }
       }

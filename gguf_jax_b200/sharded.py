@@ -16,7 +16,8 @@ import torch.distributed as dist
 from . import _backend, _lib, _matmul
 from .array import QuantizedArray
 
-__all__ = ["row_range", "shard_rows", "sharded_matmul", "gather_columns", "PeerOutput"]
+__all__ = ["row_range", "shard_rows", "sharded_matmul", "gather_columns", "PeerOutput", "TaggedExchange",
+           "TaggedVector"]
 
 
 def row_range(n_rows: int, rank: int, world: int) -> tuple[int, int]:
@@ -139,3 +140,108 @@ class PeerOutput:
                 _backend.stream_ptr(dev)))
         # a narrower product uses the front of the buffer as a dense (m, n_out) array
         return self._bufs[turn].view(-1)[: m * n_out].view(m, n_out)
+
+
+class TaggedVector:
+    """Handle to the result of one :meth:`TaggedExchange.matmul`: ``n`` tagged words in buffer
+    ``index`` of the exchange, produced by its ``serial``-th launch."""
+
+    __slots__ = ("owner", "index", "n", "serial")
+
+    def __init__(self, owner, index: int, n: int, serial: int):
+        self.owner, self.index, self.n, self.serial = owner, index, n, serial
+
+    def to_tensor(self) -> torch.Tensor:
+        """The bf16 values, once every rank's launch has finished (synchronise the stream and pass
+        a barrier first: the host has no other way to know the words have all landed)."""
+        words = self.owner._bufs[self.index][: self.n]
+        return words.view(torch.int16).view(-1, 2)[:, 0].contiguous().view(torch.bfloat16).reshape(1, self.n)
+
+
+class TaggedExchange:
+    """Chains of row-sharded batch-1 products whose outputs feed later products, with the exchange
+    inside the kernels and no flags or fences (``ggq_gemv_sharded_tagged``).
+
+    Each launch stores its rows into every rank's buffer as self-validating 32-bit words (bf16
+    value + 16-bit tag of the exchange); a later launch that takes a :class:`TaggedVector` as its
+    activation polls the words it needs until they carry the expected tag.  Buffers are used
+    round-robin: a result may be consumed by the next ``n_buffers - 2`` launches at most.  All
+    ranks must issue the same sequence of launches.  Tags are derived on the device from a
+    per-rank launch counter, so a captured CUDA graph of a whole chain can be replayed.
+    Supported: Q4_K, Q5_K and Q6_K weights at batch 1 (the tuned kernels' shapes).
+
+    Replaying a captured chain of L launches repeats its buffer sequence, so the round-robin must
+    stay intact across the seam: pick ``n_buffers`` with ``L % n_buffers == 0`` or
+    ``L % n_buffers >= 4`` (:meth:`buffers_for` does).
+    """
+
+    @staticmethod
+    def buffers_for(chain_length: int, max_back: int = 2) -> int:
+        """Smallest buffer count that keeps every reuse ``max_back + 2`` launches apart when a
+        chain of ``chain_length`` launches is replayed back to back."""
+        for nb in range(max_back + 2, 17):
+            if chain_length % nb == 0 or chain_length % nb >= max_back + 2:
+                return nb
+        return max_back + 2
+
+    def __init__(self, group, n_max: int, device=None, n_buffers: int = 4):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one NVLink domain)")
+        if n_buffers < 3:
+            raise ValueError("at least 3 buffers")
+        self.device = torch.device(device) if device is not None else _backend.default_device()
+        self.n_max = int(n_max)
+        self._bufs, self._buf_ptrs = [], []
+        for _ in range(n_buffers):
+            t = symm.empty((self.n_max,), dtype=torch.int32, device=self.device)
+            t.zero_()
+            hdl = symm.rendezvous(t, self.group)
+            self._bufs.append(t)
+            self._buf_ptrs.append((ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs]))
+        self._state = torch.zeros(64, dtype=torch.int32, device=self.device)
+        self._serial = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def matmul(self, x, w_shard: QuantizedArray) -> TaggedVector:
+        """``x @ w.T`` for this rank's rows of ``w``; ``x`` is a bf16 tensor of ``K`` elements or the
+        :class:`TaggedVector` of an earlier launch (its first ``K`` words are used)."""
+        k = w_shard.shape[1]
+        n_out = w_shard.shape[0] * self.world
+        if n_out > self.n_max:
+            raise ValueError(f"{self.world} shards of {w_shard.shape[0]} rows exceed the buffers' {self.n_max} words")
+        dev = _backend.require_cuda(w_shard.data, "sharded matmul")
+        _lib.ensure_tables(dev)
+        L = _lib.lib()
+        x_plain = x_tagged = None
+        back = 0
+        if isinstance(x, TaggedVector):
+            if x.owner is not self or x.n < k:
+                raise ValueError("x must be a result of this exchange with at least K elements")
+            back = self._serial - x.serial + 1
+            if back < 1 or back > len(self._bufs) - 2:
+                raise ValueError(f"that result is {back} launches old; its buffer may have been reused "
+                                 f"(at most {len(self._bufs) - 2} with {len(self._bufs)} buffers)")
+            x_tagged = self._bufs[x.index].data_ptr()
+        else:
+            if x.numel() != k or x.dtype != torch.bfloat16:
+                raise ValueError(f"x must be {k} bfloat16 values, got {tuple(x.shape)} {x.dtype}")
+            x = x.contiguous()
+            x_plain = x.data_ptr()
+        self._serial += 1
+        index = self._serial % len(self._bufs)
+        with torch.cuda.device(dev):
+            ws = _backend.workspace(dev, L.ggq_workspace_bytes(int(w_shard.qtype), w_shard.shape[0], k, 1))
+            _lib.check(L.ggq_gemv_sharded_tagged(
+                int(w_shard.qtype), w_shard.data.data_ptr(), w_shard.shape[0], k, x_plain, x_tagged, back,
+                self._buf_ptrs[index], self._state.data_ptr(), self.world, self.rank, n_out,
+                ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                _backend.stream_ptr(dev)))
+        return TaggedVector(self, index, n_out, self._serial)

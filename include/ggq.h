@@ -121,11 +121,30 @@ int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, const void*
  * rank has published the previous exchange, i.e. until x -- if it is the result of that exchange
  * -- is complete.  All ranks must issue the same sequence of calls.  Host arrays y_peers /
  * flag_peers are read during the call only.  Returns GGQ_UNSUPPORTED for qtype / batch
- * combinations without a publishing kernel (today: everything but Q4_K at batch 1). */
+ * combinations without a publishing kernel (today: everything but Q4_K, Q5_K and Q6_K at
+ * batch 1). */
 int32_t ggq_gemv_sharded(int32_t qtype, const void* w, int64_t N_local, int64_t K, const void* x_bf16,
                          int32_t M, void* const* y_peers, uint32_t* const* flag_peers, int32_t world,
                          int32_t rank, int64_t n_total, int32_t y_dtype, int32_t wait_previous,
                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* Row-sharded batch-1 multiply with a tagged exchange: no flags and no fences.  No counterpart in
+ * the reference.  Every output element is stored into every rank's buffer as one 32-bit word
+ * (bf16 value in the low half, a 16-bit tag of the exchange in the high half), so each word
+ * validates itself and the exchange costs one store flight.  y_peers[p] is the address, valid on
+ * THIS device, of rank p's uint32[n_total] buffer.  The activations are either plain bf16
+ * (x_bf16) or the tagged words a previous call of this function left in this rank's own buffer
+ * (x_tagged, with x_back = how many sharded launches ago that call was, 1 = the previous one);
+ * the kernel then polls each word until its tag is the expected one (bounded: GGQ_TIMEOUT via
+ * ggq_read_status).  `state` is this rank's array of (world + 2) uint32, zero-filled once, that
+ * only this function touches: it counts the exchanges, from which both tags are derived on the
+ * device, so a captured CUDA graph can be replayed.  All ranks must issue the same sequence of
+ * calls; a buffer may be reused for a new exchange once x_back_max + 2 exchanges have passed. */
+int32_t ggq_gemv_sharded_tagged(int32_t qtype, const void* w, int64_t N_local, int64_t K,
+                                const void* x_bf16, const uint32_t* x_tagged, int32_t x_back,
+                                uint32_t* const* y_peers, uint32_t* state, int32_t world,
+                                int32_t rank, int64_t n_total, void* workspace,
+                                size_t workspace_bytes, void* stream);
 
 /* Batch-1 Q4_K multiply that needs no scratch from the caller and allocates nothing.
  * No counterpart in the reference.  It exists for hosts that cannot allocate device memory

@@ -61,6 +61,48 @@ def main():
         dist.barrier()
         torch.cuda.synchronize()
         same(y, single, f"rank {rank}: fused exchange, step {step}")
+    # tagged exchange: a chain whose products feed each other (n = k), including a result consumed
+    # two launches later, then the same chain captured in a CUDA graph and replayed
+    nk = 2048
+    chain = [QT.Q4_K, QT.Q6_K, QT.Q5_K, QT.Q6_K, QT.Q4_K]
+    ws_full = [gj.QuantizedArray.from_bytes(synth.make_weight_bytes(nk, nk, qt, seed=40 + i), qt, shape=(nk, nk), device=dev)
+               for i, qt in enumerate(chain)]
+    shards = [sharded.shard_rows(w, rank, world) for w in ws_full]
+    ex = sharded.TaggedExchange(None, n_max=nk, device=dev, n_buffers=sharded.TaggedExchange.buffers_for(len(chain)))
+    x0 = torch.from_numpy(synth.make_x(1, nk, seed=50)).to(dev).to(torch.bfloat16)
+
+    def run_chain():
+        outs = [ex.matmul(x0, shards[0])]
+        outs.append(ex.matmul(outs[0], shards[1]))
+        outs.append(ex.matmul(outs[1], shards[2]))
+        outs.append(ex.matmul(outs[1], shards[3]))      # consumes a result two launches old
+        outs.append(ex.matmul(outs[3], shards[4]))
+        return outs
+
+    def check_chain(outs, what):
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        vals = [o.to_tensor().clone() for o in outs]
+        inputs = [x0, vals[0], vals[1], vals[1], vals[3]]
+        for i, (xin, w) in enumerate(zip(inputs, ws_full)):
+            # scale-free comparison: the chain's magnitudes grow with every product
+            single = kernels.fused_matmul(xin, w)
+            same(vals[i], single, f"rank {rank}: tagged chain {what}, launch {i}")
+        dist.barrier()
+
+    check_chain(run_chain(), "eager")
+    check_chain(run_chain(), "eager again")
+    st = torch.cuda.Stream(dev)
+    with torch.cuda.stream(st):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            outs = run_chain()
+    for rep in range(3):
+        with torch.cuda.stream(st):
+            g.replay()
+        st.synchronize()
+        check_chain(outs, f"graph replay {rep}")
     import ctypes
     from gguf_jax_b200 import _lib
     word = ctypes.c_int32(0)
