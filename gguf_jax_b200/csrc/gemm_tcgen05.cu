@@ -7,10 +7,15 @@
 // instruction (16..256 columns).  A CTA owns one tile of 128 weight rows x up to 256 batch
 // rows and walks K in blocks of 32 elements:
 //
-//   producer warps (16) in four groups, one per pipeline stage: a group decodes 128 x 32 weights
-//                       to float32 with the same per-qtype routines as
-//                       the decode kernel (bit-exact values, rounded to tf32), widen the
-//                       32 x M activations from bf16, and store both into shared memory in the
+//   producer warps (16) first bring the raw block bytes of 128 rows x 256 weights into a ring in
+//                       shared memory with 16-byte cp.async copies (two chunks ahead; rows of a
+//                       GGUF tensor are only 2-byte aligned in general, so a copy takes the
+//                       16-byte aligned window around the row's bytes and the decoder reads at
+//                       the row's offset in it), then decode them from there -- shared-memory
+//                       latency instead of a cache miss per block -- with the same per-qtype
+//                       routines as the decode kernel (bit-exact values, rounded to tf32), widen
+//                       the 32 x M activations from bf16 (prefetched one K block ahead), and
+//                       store both into shared memory in the
 //                       canonical K-major 128-byte-swizzled layout the MMA reads;
 //   MMA warp (1 thread) issues four tcgen05.mma.kind::tf32 (K = 8 each) per K block,
 //                       accumulating in TMEM, and tcgen05.commit hands the stage back;
@@ -30,6 +35,7 @@
 // Every wait on an mbarrier is bounded; a wait that runs out raises the device status word
 // (GGQ_TIMEOUT through ggq_read_status), lets the CTA fall through to the common exit, and
 // the TMEM allocation is always released.
+#define GGQ_DECODE_GENERIC_LOADS   // the decoders read staged blocks from shared memory
 #include "ggq_decode.cuh"
 #include "gemv.cuh"
 
@@ -39,13 +45,14 @@ namespace gemm {
 constexpr int kTileN = 128;        // weight rows per CTA (MMA M)
 constexpr int kMaxTileM = 256;     // batch rows per CTA (MMA N)
 constexpr int kBlockK = 32;        // elements per K block: 32 tf32 = one 128-byte swizzle row
-constexpr int kStages = 4;
+constexpr int kMaxStages = 4;       // MMA operand stages (fewer when the batch tile is large)
 constexpr int kProducerWarps = 16;
 constexpr int kProducers = kProducerWarps * 32;
-constexpr int kGroups = kProducerWarps / 4;   // one group of 128 threads per pipeline stage
-static_assert(kGroups == kStages, "stage j belongs to producer group j");
-constexpr int kPrefetchBytes = 1024;
+constexpr int kChunkK = 256;        // weights per row in one raw chunk
+constexpr int kKbPerChunk = kChunkK / kBlockK;
+constexpr int kRawStages = 3;       // raw chunks in shared memory: one being decoded, two in flight
 constexpr int kMaxSplits = 8;
+constexpr int kSmemLimit = 232448;
 constexpr int kThreads = (kProducerWarps + 1) * 32;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
@@ -108,15 +115,30 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
 // float32 -> tf32 container, round to nearest (ties away): the MMA ignores the low 13 bits.
 __device__ __forceinline__ float to_tf32(float v) { return __uint_as_float(__float_as_uint(v) + 0x1000u); }
 
+// Raw bytes of one row in one chunk, and the pitch of its 16-byte aligned window.
+template <int QT> constexpr int raw_row_bytes() { return kChunkK / block_elems_of(QT) * block_bytes_of(QT); }
+template <int QT> constexpr int raw_pitch() { return (raw_row_bytes<QT>() + 15 + 15) / 16 * 16; }
+
 struct Layout {
-  int a_bytes, b_bytes, stage_bytes;
-  __host__ __device__ explicit Layout(int tile_m)
-      : a_bytes(kTileN * 128), b_bytes(tile_m * 128), stage_bytes(kTileN * 128 + tile_m * 128) {}
-  __host__ __device__ int bars() const { return kStages * stage_bytes; }
-  __host__ __device__ int total() const { return bars() + 128 + 1024; }   // + barriers/flags + alignment slack
+  int a_bytes, b_bytes, stage_bytes, stages, raw_bytes;
+  __host__ __device__ Layout(int tile_m, int pitch)
+      : a_bytes(kTileN * 128), b_bytes(tile_m * 128), stage_bytes(kTileN * 128 + tile_m * 128),
+        raw_bytes(kRawStages * kTileN * pitch) {
+    stages = (kSmemLimit - raw_bytes - 256 - 1024) / stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+  }
+  __host__ __device__ int raw() const { return stages * stage_bytes; }
+  __host__ __device__ int bars() const { return raw() + raw_bytes; }
+  __host__ __device__ int total() const { return bars() + 256 + 1024; }   // + barriers/flags + alignment slack
 };
 
-template <int QT>
+__device__ __forceinline__ void cp_async16(uint32_t dst, const uint8_t* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// BIG: the batch tile has more than 128 rows, i.e. two 16-byte activation pieces per producer
+// thread and K block instead of one.
+template <int QT, bool BIG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat16* __restrict__ x, int M,
                  void* __restrict__ y, int y_dtype, const uint8_t* __restrict__ tab, int* __restrict__ status,
@@ -132,24 +154,28 @@ gemm_tf32_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat1
   const int tile_m = max(16, (m_here + 15) & ~15);           // MMA N: multiple of 16
   int tmem_cols = 32;
   while (tmem_cols < tile_m) tmem_cols <<= 1;
-  const Layout L(tile_m);
+  constexpr int RB = raw_row_bytes<QT>(), PITCH = raw_pitch<QT>();
+  const Layout L(tile_m, PITCH);
+  const int kStages = L.stages;
   const int splits = gridDim.z, split = blockIdx.z;
-  const int kb_begin = (int)((int64_t)split * (K / kBlockK) / splits);
-  const int n_kb = (int)((int64_t)(split + 1) * (K / kBlockK) / splits) - kb_begin;   // >= 1 (host guarantees)
+  // K ranges are whole chunks of 256 weights
+  const int chunk_begin = (int)((int64_t)split * (K / kChunkK) / splits);
+  const int n_chunks = (int)((int64_t)(split + 1) * (K / kChunkK) / splits) - chunk_begin;   // >= 1 (host guarantees)
+  const int n_kb = n_chunks * kKbPerChunk;
   const int64_t row_bytes = (int64_t)(K / BS) * TS;
 
   const uint32_t bars = smem_u32(smem + L.bars());
   auto full_bar = [&](int s) { return bars + 8 * s; };
   auto empty_bar = [&](int s) { return bars + 8 * (kStages + s); };
   const uint32_t done_bar = bars + 8 * (2 * kStages);
-  static_assert(8 * (2 * kStages + 1) <= 96, "barriers overlap the flags behind them");
+  static_assert(8 * (2 * kMaxStages + 1) <= 96, "barriers overlap the flags behind them");
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L.bars() + 96);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.bars() + 100);
   volatile int* last_flag = reinterpret_cast<volatile int*>(smem + L.bars() + 104);
 
   if (tid == 0) {
     for (int s = 0; s < kStages; s++) {
-      mbar_init(full_bar(s), 4);
+      mbar_init(full_bar(s), kProducerWarps);
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(done_bar, 1);
@@ -187,66 +213,100 @@ gemm_tf32_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat1
     }
   } else {
     // ------------------------------- producers -------------------------------
-    // Four groups of four warps; group j fills stage j with K blocks j, j + 4, ...  The 128 x 32
-    // weights of a block are 512 decode8 jobs: job = 4 * row + eighth, dealt so that four
-    // neighbouring lanes decode the four eighths of one row (their loads share cache lines) and a
-    // thread's four jobs are four different rows (independent loads in flight together).
-    const int r = tid & 127, group = tid >> 7;
-    const int s = group;
-    uint8_t* a_tile = smem + s * L.stage_bytes;
-    uint8_t* b_tile = a_tile + L.a_bytes;
-    const int h = r & 3;
-    const uint8_t* wrow[4];
-    bool row_ok[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      const int row = n0 + (r >> 2) + 32 * i;
-      wrow[i] = w + (int64_t)min(row, N - 1) * row_bytes;
-      row_ok[i] = row < N;
-    }
-    bool alive = true;
-    for (int kb = group, it = 0; kb < n_kb; kb += kGroups, it++) {
-      if (it > 0 && !mbar_wait(empty_bar(s), (it - 1) & 1, abort_flag, status)) { alive = false; break; }
-      const int k0 = (kb_begin + kb) * kBlockK;
-      const int64_t boff = (int64_t)(k0 / BS) * TS;
-      // pull the rows' bytes of later K blocks towards L2 while this block is decoded
-      if (boff + kPrefetchBytes < row_bytes)
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow[h] + boff + kPrefetchBytes));
-      float v[4][8];
-#pragma unroll
-      for (int i = 0; i < 4; i++) {
-        if (row_ok[i]) {
-          Dec<QT>::run(wrow[i] + boff, ((k0 % BS) >> 3) + h, tab, v[i]);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; e++) v[i][e] = 0.f;
-        }
+    // Thread (r, h): weight row r of the tile, eighth h of a 32-weight K block; it also copies
+    // pieces h, h + 4, ... of row r's raw window.
+    const int r = tid >> 2, h = tid & 3;
+    const int row = min(n0 + r, N - 1);                       // rows past the end repeat the last one (never stored)
+    const uint8_t* wsrc = w + (int64_t)row * row_bytes + (int64_t)chunk_begin * RB;
+    // reads stop at the 16-byte boundary at or after the end of the tensor (any device allocation
+    // extends that far)
+    const uint8_t* const w_stop = w + (((int64_t)N * row_bytes + 15) & ~(int64_t)15);
+    uint8_t* const raw_ring = smem + L.raw();
+    auto issue_chunk = [&](int c) {
+      if (c < n_chunks) {
+        const uint8_t* p = wsrc + (int64_t)c * RB;
+        const int skew = (int)((uintptr_t)p & 15);
+        const uint8_t* p16 = p - skew;
+        const int pieces = (skew + RB + 15) >> 4;
+        const uint32_t dst = smem_u32(raw_ring + ((c % kRawStages) * kTileN + r) * PITCH);
+        for (int q = h; q < pieces; q += 4)
+          if (p16 + 16 * q + 16 <= w_stop) cp_async16(dst + 16 * q, p16 + 16 * q);
       }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    issue_chunk(0);
+    issue_chunk(1);
+    // activations, fetched XD K blocks ahead into a small register ring (the loads come from L2
+    // and a K block is only a few hundred cycles of work)
+    constexpr int XP = BIG ? 2 : 1, XD = BIG ? 2 : 4;
+    const int k_first = chunk_begin * kChunkK;
+    uint4 xr[XD][XP];
+    auto fetch_x = [&](int kb, uint4 (&dst)[XP]) {
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const int rr = (r >> 2) + 32 * i;
-        *reinterpret_cast<float4*>(a_tile + swz(rr, 2 * h)) =
-            make_float4(to_tf32(v[i][0]), to_tf32(v[i][1]), to_tf32(v[i][2]), to_tf32(v[i][3]));
-        *reinterpret_cast<float4*>(a_tile + swz(rr, 2 * h + 1)) =
-            make_float4(to_tf32(v[i][4]), to_tf32(v[i][5]), to_tf32(v[i][6]), to_tf32(v[i][7]));
-      }
-      // B: widen the activations; chunk q = 8 consecutive k of one batch row
-      for (int q = r; q < tile_m * 4; q += 128) {
+      for (int u = 0; u < XP; u++) {
+        const int q = tid + u * kProducers;
         const int mr = q >> 2, part = q & 3;
-        uint4 u = make_uint4(0, 0, 0, 0);
-        if (mr < m_here) u = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)(m0 + mr) * K + k0) + part);
-        *reinterpret_cast<float4*>(b_tile + swz(mr, 2 * part)) =
-            make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u),
-                        __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xFFFF0000u));
-        *reinterpret_cast<float4*>(b_tile + swz(mr, 2 * part + 1)) =
-            make_float4(__uint_as_float(u.z << 16), __uint_as_float(u.z & 0xFFFF0000u),
-                        __uint_as_float(u.w << 16), __uint_as_float(u.w & 0xFFFF0000u));
+        dst[u] = make_uint4(0, 0, 0, 0);
+        if (q < tile_m * 4 && mr < m_here && kb < n_kb)
+          dst[u] = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)(m0 + mr) * K + k_first + kb * kBlockK) + part);
       }
-      // make the generic-proxy stores visible to the tensor core, then one arrival per warp
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(full_bar(s));
+    };
+#pragma unroll
+    for (int d = 0; d < XD; d++) fetch_x(d, xr[d]);
+    bool alive = true;
+    int kb = 0;
+    for (int c = 0; c < n_chunks; c++) {
+      // every producer thread passes every one of these barriers, also after a wait has given up
+      asm volatile("cp.async.wait_group 1;" ::: "memory");    // my copies of chunk c have landed
+      asm volatile("bar.sync 2, %0;" ::"n"(kProducers) : "memory");   // everybody's have; chunk c-1 is decoded
+      issue_chunk(c + 2);                                      // into the slot chunk c-1 occupied
+      if (!alive) continue;
+      const uint8_t* rawrow = raw_ring + ((c % kRawStages) * kTileN + r) * PITCH +
+                              ((uintptr_t)(wsrc + (int64_t)c * RB) & 15);
+#pragma unroll
+      for (int k8 = 0; k8 < kKbPerChunk; k8++, kb++) {
+        const int s = kb % kStages, it = kb / kStages;
+        if (it > 0 && !mbar_wait(empty_bar(s), (it - 1) & 1, abort_flag, status)) { alive = false; break; }
+        uint8_t* a_tile = smem + s * L.stage_bytes;
+        uint8_t* b_tile = a_tile + L.a_bytes;
+        // A: eight weights of row r
+        {
+          const int e = k8 * kBlockK + 8 * h;                  // element within the chunk
+          float v[8];
+          Dec<QT>::run(rawrow + (e / BS) * TS, (e % BS) >> 3, tab, v);
+          *reinterpret_cast<float4*>(a_tile + swz(r, 2 * h)) =
+              make_float4(to_tf32(v[0]), to_tf32(v[1]), to_tf32(v[2]), to_tf32(v[3]));
+          *reinterpret_cast<float4*>(a_tile + swz(r, 2 * h + 1)) =
+              make_float4(to_tf32(v[4]), to_tf32(v[5]), to_tf32(v[6]), to_tf32(v[7]));
+        }
+        // B: widen the activations; piece q = 8 consecutive k of one batch row
+#pragma unroll
+        for (int d = 0; d < XD; d++) {
+          if ((k8 % XD) == d) {                              // k8 is a compile-time constant after unrolling
+#pragma unroll
+            for (int u = 0; u < XP; u++) {
+              const int q = tid + u * kProducers;
+              if (q < tile_m * 4) {
+                const int mr = q >> 2, part = q & 3;
+                const uint4 xv = xr[d][u];
+                *reinterpret_cast<float4*>(b_tile + swz(mr, 2 * part)) =
+                    make_float4(__uint_as_float(xv.x << 16), __uint_as_float(xv.x & 0xFFFF0000u),
+                                __uint_as_float(xv.y << 16), __uint_as_float(xv.y & 0xFFFF0000u));
+                *reinterpret_cast<float4*>(b_tile + swz(mr, 2 * part + 1)) =
+                    make_float4(__uint_as_float(xv.z << 16), __uint_as_float(xv.z & 0xFFFF0000u),
+                                __uint_as_float(xv.w << 16), __uint_as_float(xv.w & 0xFFFF0000u));
+              }
+            }
+            fetch_x(kb + XD, xr[d]);
+          }
+        }
+        // make the generic-proxy stores visible to the tensor core, then one arrival per warp
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar(s));
+      }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     // ------------------------------- epilogue -------------------------------
     // A warp may read TMEM lanes 32 (warp % 4) .. + 31; the four warp groups deal the batch
     // columns among themselves in chunks of 8.
@@ -312,26 +372,33 @@ static cudaError_t launch(const uint8_t* w, int64_t N, int64_t K, const void* x,
                           const uint8_t* tab, int* status, int splits, float* partials, int* counters,
                           cudaStream_t st) {
   const int tile_m_max = M >= kMaxTileM ? kMaxTileM : ((M + 15) & ~15) < 16 ? 16 : ((M + 15) & ~15);
-  const int smem = Layout(tile_m_max).total();
+  const Layout lay(tile_m_max, raw_pitch<QT>());
+  if (lay.stages < 2) return cudaErrorInvalidValue;
+  const int smem = lay.total();
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<QT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Layout(kMaxTileM).total());
+    cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<QT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_tf32_kernel<QT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
   dim3 grid((unsigned)((N + kTileN - 1) / kTileN), (unsigned)((M + kMaxTileM - 1) / kMaxTileM), (unsigned)splits);
-  gemm_tf32_kernel<QT><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, (const __nv_bfloat16*)x, M, y, y_dtype, tab,
-                                                     status, partials, counters);
+  if (tile_m_max > 128)
+    gemm_tf32_kernel<QT, true><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, (const __nv_bfloat16*)x, M, y, y_dtype,
+                                                             tab, status, partials, counters);
+  else
+    gemm_tf32_kernel<QT, false><<<grid, kThreads, smem, st>>>(w, (int)N, (int)K, (const __nv_bfloat16*)x, M, y, y_dtype,
+                                                              tab, status, partials, counters);
   return cudaPeekAtLastError();
 }
 
 }  // namespace gemm
 
 bool gemm_applicable(const TypeInfo* ti, int64_t N, int64_t K, int M) {
-  return ti && ti->block_elems >= 32 && K % 32 == 0 && K % ti->block_elems == 0 && N >= 1 && N < (1ll << 31) - 256 &&
+  return ti && ti->block_elems >= 32 && K % gemm::kChunkK == 0 && N >= 1 && N < (1ll << 31) - 256 &&
          K < (1ll << 31) && M >= 1 && (int64_t)M * N < (1ll << 40);
 }
 
@@ -340,10 +407,10 @@ bool gemm_applicable(const TypeInfo* ti, int64_t N, int64_t K, int M) {
 int gemm_splits(int64_t N, int64_t K, int M, int sm_count) {
   if (sm_count <= 0) sm_count = 148;
   const int64_t tiles = ((N + gemm::kTileN - 1) / gemm::kTileN) * ((M + gemm::kMaxTileM - 1) / gemm::kMaxTileM);
-  const int64_t n_kb = K / gemm::kBlockK;
+  const int64_t n_chunks = K / gemm::kChunkK;
   int best = 1;
   double best_cost = 1e30;
-  for (int s = 1; s <= gemm::kMaxSplits && s * 8 <= n_kb; s++) {
+  for (int s = 1; s <= gemm::kMaxSplits && s * 2 <= n_chunks; s++) {
     const double waves = (double)((tiles * s + sm_count - 1) / sm_count);
     const double cost = waves / s + 0.04 * s;
     if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }

@@ -7,6 +7,8 @@ namespace {
 constexpr int kGemvMaxBatch = 16;
 // From this batch on the tensor-core small-batch kernel beats the per-element FMA kernel.
 constexpr int kMmaMinBatch = 2;
+// Up to this batch the tuned batch-1 kernels are simply launched once per batch row.
+constexpr int kTunedMaxRepeat = 2;
 // Measured on B200 the tcgen05 kernel behind ggq_gemm is still slower than the decode kernel
 // followed by a library bf16 GEMM (its producers wait on global loads), so
 // ggq_fused_batch_limit keeps the router at the small-batch cap and ggq_gemm is reached only
@@ -66,21 +68,27 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
     return fail(GGQ_NO_TABLES, "ggq_gemv: call ggq_set_tables(%d, ...) before using qtype %d", dev, qtype);
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t err;
-  if (qtype == QT_Q4_K && gemv_q4k_applicable(N, K, M, w, x_bf16) && workspace &&
-      workspace_bytes >= gemv_q4k_workspace_bytes(N, kMaxSmCount) && (uintptr_t)workspace % 256 == 0 &&
-      sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount) {
-    err = gemv_q4k((const uint8_t*)w, N, K, x_bf16, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev),
-                   device_status_word(dev), st);
-  } else if (qtype == QT_Q5_K && gemv_q5k_applicable(N, K, M, w, x_bf16) && workspace &&
-             workspace_bytes >= gemv_q4k_workspace_bytes(N, kMaxSmCount) && (uintptr_t)workspace % 256 == 0 &&
-             sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount) {
-    err = gemv_q5k((const uint8_t*)w, N, K, x_bf16, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev),
-                   device_status_word(dev), st);
-  } else if (qtype == QT_Q6_K && gemv_q6k_applicable(N, K, M, w, x_bf16) && workspace &&
-             workspace_bytes >= gemv_q4k_workspace_bytes(N, kMaxSmCount) && (uintptr_t)workspace % 256 == 0 &&
-             sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount) {
-    err = gemv_q6k((const uint8_t*)w, N, K, x_bf16, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev),
-                   device_status_word(dev), st);
+  // The tuned batch-1 kernels (Q4_K, Q5_K, Q6_K).  Two or three batch rows are served by that
+  // many launches of the batch-1 kernel, which is still faster than the small-batch kernel
+  // (measured: its cost is about three batch-1 launches whatever the batch).
+  const int y_item = y_dtype == GGQ_F32 ? 4 : 2;
+  const bool scratch_ok = workspace && workspace_bytes >= gemv_q4k_workspace_bytes(N, kMaxSmCount) &&
+                          (uintptr_t)workspace % 256 == 0 && sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount;
+  const bool rows_ok = M <= kTunedMaxRepeat && (M == 1 || ((K * 2) % 16 == 0 && (N * y_item) % 2 == 0));
+  using Tuned = cudaError_t (*)(const uint8_t*, int64_t, int64_t, const void*, void*, int, void*, size_t, int, int*,
+                                cudaStream_t, const PeerPublish*);
+  Tuned tuned = nullptr;
+  if (scratch_ok && rows_ok) {
+    if (qtype == QT_Q4_K && gemv_q4k_applicable(N, K, 1, w, x_bf16)) tuned = gemv_q4k;
+    else if (qtype == QT_Q5_K && gemv_q5k_applicable(N, K, 1, w, x_bf16)) tuned = gemv_q5k;
+    else if (qtype == QT_Q6_K && gemv_q6k_applicable(N, K, 1, w, x_bf16)) tuned = gemv_q6k;
+  }
+  if (tuned) {
+    err = cudaSuccess;
+    for (int m = 0; m < M && err == cudaSuccess; m++)
+      err = tuned((const uint8_t*)w, N, K, (const uint8_t*)x_bf16 + (size_t)m * K * 2,
+                  (uint8_t*)y + (size_t)m * N * y_item, y_dtype, workspace, workspace_bytes, sm_count_of(dev),
+                  device_status_word(dev), st, nullptr);
   } else if (gemv_mma_applicable(ti, N, K, M) && M >= kMmaMinBatch) {
     err = gemv_mma(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, st);
   } else {
@@ -204,13 +212,12 @@ extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, 
                 (long long)N, (long long)K, M, ti->block_elems);
   if (!gemm_applicable(ti, N, K, M))
     return fail(GGQ_UNSUPPORTED, "ggq_gemm: shape N=%lld K=%lld M=%d is outside the tensor-core kernel's range "
-                "(K must be a multiple of 32)", (long long)N, (long long)K, M);
+                "(K must be a multiple of 256)", (long long)N, (long long)K, M);
   if (y_dtype != GGQ_F32 && y_dtype != GGQ_BF16 && y_dtype != GGQ_F16)
     return fail(GGQ_BAD_DTYPE, "ggq_gemm: y_dtype %d", y_dtype);
   if (!w || !x_bf16 || !y) return fail(GGQ_MISALIGNED, "ggq_gemm: null pointer");
   if ((uintptr_t)x_bf16 % 16) return fail(GGQ_MISALIGNED, "ggq_gemm: x must be 16-byte aligned");
-  if ((uintptr_t)w % block_alignment(ti))
-    return fail(GGQ_MISALIGNED, "ggq_gemm: w must be %d-byte aligned for qtype %d", block_alignment(ti), qtype);
+  if ((uintptr_t)w % 16) return fail(GGQ_MISALIGNED, "ggq_gemm: w must be 16-byte aligned");
   int dev = 0;
   cudaGetDevice(&dev);
   const uint8_t* tab = device_tables(dev);

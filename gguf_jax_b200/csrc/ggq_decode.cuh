@@ -15,9 +15,23 @@
 
 #include "ggq_common.cuh"
 
-namespace ggq {
+// Where the block bytes live.  By default they are read from global memory through the
+// read-only path (__ldg).  A translation unit that stages raw blocks in shared memory first
+// (gemm_tcgen05.cu) defines GGQ_DECODE_GENERIC_LOADS before including this header and gets the
+// same decoders with plain generic loads, which work on shared and global addresses alike.
+// The two flavours live in different inline namespaces, so they are different entities.
+#ifdef GGQ_DECODE_GENERIC_LOADS
+#define GGQ_LD(p) (*(p))
+#define GGQ_DEC_NS dec_generic_loads
+#else
+#define GGQ_LD(p) __ldg(p)
+#define GGQ_DEC_NS dec_global_loads
+#endif
 
-__device__ __forceinline__ uint32_t ldb(const uint8_t* p) { return __ldg(p); }
+namespace ggq {
+inline namespace GGQ_DEC_NS {
+
+__device__ __forceinline__ uint32_t ldb(const uint8_t* p) { return GGQ_LD(p); }
 __device__ __forceinline__ uint32_t ld16(const uint8_t* p) { return ldb(p) | (ldb(p + 1) << 8); }
 __device__ __forceinline__ uint32_t ld32(const uint8_t* p) {
   return ldb(p) | (ldb(p + 1) << 8) | (ldb(p + 2) << 16) | (ldb(p + 3) << 24);
@@ -29,14 +43,14 @@ __device__ __forceinline__ uint32_t ld32(const uint8_t* p) {
 template <int ALIGN>
 __device__ __forceinline__ uint2 ld8(const uint8_t* p) {
   if constexpr (ALIGN >= 8) {
-    return __ldg(reinterpret_cast<const uint2*>(p));
+    return GGQ_LD(reinterpret_cast<const uint2*>(p));
   } else if constexpr (ALIGN >= 4) {
     const uint32_t* q = reinterpret_cast<const uint32_t*>(p);
-    return make_uint2(__ldg(q), __ldg(q + 1));
+    return make_uint2(GGQ_LD(q), GGQ_LD(q + 1));
   } else if constexpr (ALIGN >= 2) {
     const unsigned short* q = reinterpret_cast<const unsigned short*>(p);
-    return make_uint2((uint32_t)__ldg(q) | ((uint32_t)__ldg(q + 1) << 16),
-                      (uint32_t)__ldg(q + 2) | ((uint32_t)__ldg(q + 3) << 16));
+    return make_uint2((uint32_t)GGQ_LD(q) | ((uint32_t)GGQ_LD(q + 1) << 16),
+                      (uint32_t)GGQ_LD(q + 2) | ((uint32_t)GGQ_LD(q + 3) << 16));
   } else {
     return make_uint2(ld32(p), ld32(p + 4));
   }
@@ -129,7 +143,7 @@ template <> struct Dec<QT_Q5_1> {
 };
 template <> struct Dec<QT_Q8_0> {
   __device__ static void run(const uint8_t* b, int g, const uint8_t*, float* o) {
-    float d = h2f(__ldg(reinterpret_cast<const unsigned short*>(b)));
+    float d = h2f(GGQ_LD(reinterpret_cast<const unsigned short*>(b)));
     const uint2 q = ld8<2>(b + 2 + 8 * g);
 #pragma unroll
     for (int i = 0; i < 8; i++) o[i] = __fmul_rn(i2f((int8_t)byte_of(q, i)), d);
@@ -218,7 +232,7 @@ __device__ __forceinline__ void scale_min_k4_words(const uint4& h, int k, int& s
 }
 template <> struct Dec<QT_Q4_K> {
   __device__ static void run(const uint8_t* b, int g, const uint8_t*, float* o) {
-    const uint4 h = __ldg(reinterpret_cast<const uint4*>(b));
+    const uint4 h = GGQ_LD(reinterpret_cast<const uint4*>(b));
     const float d = h2f(h.x & 0xFFFF), dmin = h2f(h.x >> 16);
     int k = g >> 2, sc, mn;
     scale_min_k4_words(h, k, sc, mn);
@@ -231,7 +245,7 @@ template <> struct Dec<QT_Q4_K> {
 };
 template <> struct Dec<QT_Q5_K> {
   __device__ static void run(const uint8_t* b, int g, const uint8_t*, float* o) {
-    const uint4 h = __ldg(reinterpret_cast<const uint4*>(b));
+    const uint4 h = GGQ_LD(reinterpret_cast<const uint4*>(b));
     const float d = h2f(h.x & 0xFFFF), dmin = h2f(h.x >> 16);
     int k = g >> 2, sc, mn;
     scale_min_k4_words(h, k, sc, mn);
@@ -249,7 +263,7 @@ template <> struct Dec<QT_Q5_K> {
 // Q6_K blocks are 210 bytes: 2-byte aligned, all offsets below are even.
 template <> struct Dec<QT_Q6_K> {
   __device__ static void run(const uint8_t* b, int g, const uint8_t*, float* o) {
-    float d = h2f(__ldg(reinterpret_cast<const unsigned short*>(b + 208)));
+    float d = h2f(GGQ_LD(reinterpret_cast<const unsigned short*>(b + 208)));
     float dl = __fmul_rn(d, i2f((int8_t)ldb(b + 192 + (g >> 1))));
     int c = g >> 2, t0 = 8 * (g & 3);
     const uint2 ql = ld8<2>(b + 64 * (c >> 2) + 32 * (c & 1) + t0);
@@ -417,4 +431,5 @@ inline bool dispatch_block_qtype(int qtype, F&& f) {
   }
 }
 
+}  // inline namespace
 }  // namespace ggq
