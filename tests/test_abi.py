@@ -57,3 +57,36 @@ def test_caps_and_argument_errors_without_gpu(built_lib):
     assert built_lib.ggq_dequant(int(QT.Q4_K), None, -1, None, 0, None) == 2
     with pytest.raises(_lib.GGQError):
         _lib.check(built_lib.ggq_dequant(int(QT.I8), None, 1, None, 0, None))
+
+
+def test_sharded_entry_points_validate_before_any_cuda_call(built_lib):
+    import ctypes
+    ptrs = (ctypes.c_void_p * 8)()
+    # rank outside the world, too many ranks
+    assert built_lib.ggq_gemv_sharded(int(QT.Q4_K), None, 64, 256, None, 1, ptrs, ptrs, 9, 0, 576, 1, 0, None, 0, None) == 2
+    assert built_lib.ggq_gemv_sharded(int(QT.Q4_K), None, 64, 256, None, 1, ptrs, ptrs, 2, 2, 128, 1, 0, None, 0, None) == 2
+    # the shards do not fit the output
+    assert built_lib.ggq_gemv_sharded(int(QT.Q4_K), None, 64, 256, None, 1, ptrs, ptrs, 2, 0, 100, 1, 0, None, 0, None) == 2
+    assert built_lib.ggq_gemv_sharded_tagged(int(QT.Q4_K), None, 64, 256, None, None, 1, ptrs, None, 9, 0, 576,
+                                             None, 0, None) == 2
+    assert built_lib.ggq_gemv_sharded_tagged(int(QT.I8), None, 64, 256, None, None, 1, ptrs, None, 2, 0, 128,
+                                             None, 0, None) == 1
+    # neither plain nor tagged activations
+    assert built_lib.ggq_gemv_sharded_tagged(int(QT.Q4_K), None, 64, 256, None, None, 1, ptrs, None, 2, 0, 128,
+                                             None, 0, None) == 3   # MISALIGNED (null pointer)
+    assert b"null pointer" in built_lib.ggq_last_error()
+
+
+def test_workspace_sizes(built_lib):
+    # batch-1 tuned kernels: fixed partial area + one counter per 32 rows
+    small = built_lib.ggq_workspace_bytes(int(QT.Q4_K), 4096, 4096, 1)
+    assert small >= 131072 + 4096 // 32 * 4 and small % 256 == 0
+    assert built_lib.ggq_workspace_bytes(int(QT.Q6_K), 4096, 4096, 1) == small
+    assert built_lib.ggq_workspace_bytes(int(QT.Q5_K), 4096, 4096, 1) == small
+    assert built_lib.ggq_workspace_bytes(int(QT.Q8_0), 4096, 4096, 1) == 0
+    # the tensor-core kernel cuts K when there are few row tiles and then needs partial tiles
+    # (sized without a device here, i.e. for 148 SMs)
+    big = built_lib.ggq_workspace_bytes(int(QT.Q8_0), 1024, 8192, 64)
+    assert big == 0 or big >= (4 << 20) + 2 * 64 * 1024 * 4
+    # many row tiles: one K range per tile, no scratch
+    assert built_lib.ggq_workspace_bytes(int(QT.Q8_0), 148 * 128 * 4, 1024, 64) == 0
