@@ -7,8 +7,9 @@ namespace {
 constexpr int kGemvMaxBatch = 16;
 // From this batch on the tensor-core small-batch kernel beats the per-element FMA kernel.
 constexpr int kMmaMinBatch = 2;
-// Up to this batch the tuned batch-1 kernels are simply launched once per batch row.
-constexpr int kTunedMaxRepeat = 2;
+// Up to this batch the tuned batch-1 kernels are simply launched once per batch row: measured on
+// B200 the small-batch kernel costs about 3 (Q4_K) to 4.6 (Q6_K) batch-1 launches on large weights.
+constexpr int tuned_max_repeat(int qtype) { return qtype == QT_Q4_K ? 3 : 4; }
 // Measured on B200 the tcgen05 kernel behind ggq_gemm is still slower than the decode kernel
 // followed by a library bf16 GEMM (its producers wait on global loads), so
 // ggq_fused_batch_limit keeps the router at the small-batch cap and ggq_gemm is reached only
@@ -68,13 +69,12 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
     return fail(GGQ_NO_TABLES, "ggq_gemv: call ggq_set_tables(%d, ...) before using qtype %d", dev, qtype);
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t err;
-  // The tuned batch-1 kernels (Q4_K, Q5_K, Q6_K).  Two or three batch rows are served by that
-  // many launches of the batch-1 kernel, which is still faster than the small-batch kernel
-  // (measured: its cost is about three batch-1 launches whatever the batch).
+  // The tuned batch-1 kernels (Q4_K, Q5_K, Q6_K).  A few batch rows are served by that many
+  // launches of the batch-1 kernel, which is still faster than the small-batch kernel.
   const int y_item = y_dtype == GGQ_F32 ? 4 : 2;
   const bool scratch_ok = workspace && workspace_bytes >= gemv_q4k_workspace_bytes(N, kMaxSmCount) &&
                           (uintptr_t)workspace % 256 == 0 && sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount;
-  const bool rows_ok = M <= kTunedMaxRepeat && (M == 1 || ((K * 2) % 16 == 0 && (N * y_item) % 2 == 0));
+  const bool rows_ok = M <= tuned_max_repeat(qtype) && (M == 1 || ((K * 2) % 16 == 0 && (N * y_item) % 2 == 0));
   using Tuned = cudaError_t (*)(const uint8_t*, int64_t, int64_t, const void*, void*, int, void*, size_t, int, int*,
                                 cudaStream_t, const PeerPublish*);
   Tuned tuned = nullptr;
