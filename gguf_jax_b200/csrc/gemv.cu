@@ -91,6 +91,8 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
                   device_status_word(dev), st, nullptr);
   } else if (gemv_mma_applicable(ti, N, K, M) && M >= kMmaMinBatch) {
     err = gemv_mma(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, st);
+  } else if (gemv_stream_applicable(ti, N, K, M, w, x_bf16)) {
+    err = gemv_stream(ti, (const uint8_t*)w, N, K, x_bf16, y, y_dtype, tab, st);
   } else {
     err = gemv_generic(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, st);
   }

@@ -16,6 +16,12 @@ __device__ __forceinline__ void store_out(void* y, int y_dtype, int64_t idx, flo
 cudaError_t gemv_generic(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K, const void* x, int M,
                          void* y, int y_dtype, const uint8_t* tab, cudaStream_t st);
 
+// Batch 1, any block qtype, K a multiple of 256, 16-byte aligned weight: warp per row with the raw
+// blocks streamed through shared memory (gemv_stream.cu).
+bool gemv_stream_applicable(const TypeInfo* ti, int64_t N, int64_t K, int M, const void* w, const void* x);
+cudaError_t gemv_stream(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K, const void* x, void* y,
+                        int y_dtype, const uint8_t* tab, cudaStream_t st);
+
 // Row-sharded output over several GPUs of one node (one process per GPU).  Instead of writing
 // y into a local buffer and all-gathering it, a kernel can store its slice of the output rows
 // straight into every peer's copy of y (peer-mapped pointers over NVLink) and, when the whole
