@@ -7,9 +7,13 @@ namespace {
 constexpr int kGemvMaxBatch = 16;
 // From this batch on the tensor-core small-batch kernel beats the per-element FMA kernel.
 constexpr int kMmaMinBatch = 2;
-// Up to this batch the tuned batch-1 kernels are simply launched once per batch row: measured on
-// B200 the small-batch kernel costs about 3 (Q4_K) to 4.6 (Q6_K) batch-1 launches on large weights.
-constexpr int tuned_max_repeat(int qtype) { return qtype == QT_Q4_K ? 3 : 4; }
+// Up to this batch the tuned batch-1 kernels are simply launched once per batch row.  Measured on
+// B200 the small-batch kernel costs 1.4 (12 MB weight) to 3 (130 MB) batch-1 launches for Q4_K and
+// Q5_K, and 3.3 (50 MB) to 4.8 (190 MB) for Q6_K.
+inline int tuned_max_repeat(int qtype, int64_t weight_bytes) {
+  if (qtype == QT_Q6_K) return weight_bytes < (24ll << 20) ? 2 : weight_bytes < (100ll << 20) ? 3 : 4;
+  return weight_bytes < (24ll << 20) ? 1 : weight_bytes < (80ll << 20) ? 2 : 3;
+}
 // Measured on B200 the tcgen05 kernel behind ggq_gemm is still slower than the decode kernel
 // followed by a library bf16 GEMM (its producers wait on global loads), so
 // ggq_fused_batch_limit keeps the router at the small-batch cap and ggq_gemm is reached only
@@ -74,7 +78,7 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
   const int y_item = y_dtype == GGQ_F32 ? 4 : 2;
   const bool scratch_ok = workspace && workspace_bytes >= gemv_q4k_workspace_bytes(N, kMaxSmCount) &&
                           (uintptr_t)workspace % 256 == 0 && sm_count_of(dev) > 0 && sm_count_of(dev) <= kMaxSmCount;
-  const bool rows_ok = M <= tuned_max_repeat(qtype) && (M == 1 || ((K * 2) % 16 == 0 && (N * y_item) % 2 == 0));
+  const bool rows_ok = M <= tuned_max_repeat(qtype, N * (K / ti->block_elems) * ti->block_bytes) && (M == 1 || ((K * 2) % 16 == 0 && (N * y_item) % 2 == 0));
   using Tuned = cudaError_t (*)(const uint8_t*, int64_t, int64_t, const void*, void*, int, void*, size_t, int, int*,
                                 cudaStream_t, const PeerPublish*);
   Tuned tuned = nullptr;

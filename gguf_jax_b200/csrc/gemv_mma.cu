@@ -118,29 +118,32 @@ gemv_mma_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat16
 }
 
 // ---------------------------------------------------------------------------------------------
-// Q4_K, 2 <= M <= 16, without the float32 detour: the 4-bit codes go to the tensor cores as exact
+// Q4_K and Q5_K, 2 <= M <= 16, without the float32 detour: the 4-bit codes go to the tensor cores as exact
 // bf16 integers (0x000v = v * 2^-133; the high nibbles as 16 v), one MMA layer instead of three,
 // and the float32 scales are applied to the 32-weight partial sums:
 //     y[m] += (d * sc) * sum(q * x[m]) - (dmin * mn) * sum(x[m])      per sub-block,
 // with sum(x[m]) from a second MMA against an all-ones A operand.  Activations are multiplied by
 // 2^64 on the way in so that the products are normal float32 numbers (valid for activation
 // magnitudes from about 2^-50 to 2^62).  Warp j of a CTA takes sub-block j of every superblock.
-template <int NCG>
+// Q5: the block is Q5_K (176 bytes: the same header, then 32 bytes of fifth bits, then the nibbles)
+// and the code is nibble | bit << 4, assembled per byte before it is spread into bf16 pairs.
+template <int NCG, bool Q5>
 __global__ void __launch_bounds__(kThreads)
-gemv_mma_q4k_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat16* __restrict__ x, int M,
+gemv_mma_q45k_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat16* __restrict__ x, int M,
                     void* __restrict__ y, int y_dtype) {
   __shared__ float red[kWarps][NCG][4][32];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
   const int n_sb = K / 256;
-  const int64_t row_bytes = (int64_t)n_sb * 144;
+  constexpr int TS = Q5 ? 176 : 144, QS = Q5 ? 48 : 16;
+  const int64_t row_bytes = (int64_t)n_sb * TS;
   const uint8_t* w0 = w + (int64_t)min(n0 + g, N - 1) * row_bytes;
   const uint8_t* w1 = w + (int64_t)min(n0 + g + 8, N - 1) * row_bytes;
   const int sbk = warp, pair = sbk >> 1;
   const bool high = sbk & 1;
   const uint32_t mask = high ? 0x00F000F0u : 0x000F000Fu;
-  const float up_codes = high ? 0x1p65f : 0x1p69f;     // 2^(133 - 64), and 1/16 for the high nibbles
+  const float up_codes = (high && !Q5) ? 0x1p65f : 0x1p69f;   // 2^(133 - 64); Q4_K keeps high nibbles as 16 q
   const __nv_bfloat162 x_up = __floats2bfloat162_rn(0x1p64f, 0x1p64f);
   const uint32_t ones = 0x3F803F80u;                    // bf16 (1.0, 1.0)
 
@@ -150,16 +153,22 @@ gemv_mma_q4k_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bflo
 #pragma unroll
     for (int i = 0; i < 4; i++) acc[c][i] = 0.f;
 
-  // the loads of superblock b + 1 are issued before superblock b is multiplied
-  struct Raw { uint4 h0, h1; uint2 q0, q1; uint4 xq[NCG]; };
+  // the loads of superblock b + 1 are issued before superblock b is multiplied (a deeper register
+  // pipeline measured slower: the registers it takes cost more occupancy than the latency it hides)
+  struct Raw { uint4 h0, h1; uint2 q0, q1, e0, e1; uint4 xq[NCG]; };
   auto load = [&](int b) {
     Raw r;
-    const uint8_t* blk0 = w0 + (int64_t)b * 144;
-    const uint8_t* blk1 = w1 + (int64_t)b * 144;
+    const uint8_t* blk0 = w0 + (int64_t)b * TS;
+    const uint8_t* blk1 = w1 + (int64_t)b * TS;
     r.h0 = __ldg(reinterpret_cast<const uint4*>(blk0));
     r.h1 = __ldg(reinterpret_cast<const uint4*>(blk1));
-    r.q0 = __ldg(reinterpret_cast<const uint2*>(blk0 + 16 + 32 * pair + 8 * t));
-    r.q1 = __ldg(reinterpret_cast<const uint2*>(blk1 + 16 + 32 * pair + 8 * t));
+    r.q0 = __ldg(reinterpret_cast<const uint2*>(blk0 + QS + 32 * pair + 8 * t));
+    r.q1 = __ldg(reinterpret_cast<const uint2*>(blk1 + QS + 32 * pair + 8 * t));
+    r.e0 = r.e1 = make_uint2(0, 0);
+    if constexpr (Q5) {
+      r.e0 = __ldg(reinterpret_cast<const uint2*>(blk0 + 16 + 8 * t));
+      r.e1 = __ldg(reinterpret_cast<const uint2*>(blk1 + 16 + 8 * t));
+    }
 #pragma unroll
     for (int c = 0; c < NCG; c++) {
       const int m = 8 * c + g;                          // the batch row this lane feeds as B column g
@@ -193,8 +202,17 @@ gemv_mma_q4k_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bflo
       ndm[rr] = -__fmul_rn(__fmul_rn(__high2float(dd), (float)mn), 0x1p-64f);
     }
     // bytes (0,2) of a word fill k-slots 2t, 2t+1, bytes (1,3) fill k-slots 2t+8, 2t+9
-    const uint32_t a00 = q0.x & mask, a01 = q1.x & mask, a02 = (q0.x >> 8) & mask, a03 = (q1.x >> 8) & mask;
-    const uint32_t a10 = q0.y & mask, a11 = q1.y & mask, a12 = (q0.y >> 8) & mask, a13 = (q1.y >> 8) & mask;
+    uint32_t a00, a01, a02, a03, a10, a11, a12, a13;
+    if constexpr (Q5) {
+      const int ns = high ? 4 : 0;
+      auto code = [&](uint32_t q, uint32_t e) { return ((q >> ns) & 0x0F0F0F0Fu) | (((e >> sbk) & 0x01010101u) << 4); };
+      const uint32_t c0x = code(q0.x, cur.e0.x), c1x = code(q1.x, cur.e1.x), c0y = code(q0.y, cur.e0.y), c1y = code(q1.y, cur.e1.y);
+      a00 = c0x & 0x00FF00FFu; a01 = c1x & 0x00FF00FFu; a02 = (c0x >> 8) & 0x00FF00FFu; a03 = (c1x >> 8) & 0x00FF00FFu;
+      a10 = c0y & 0x00FF00FFu; a11 = c1y & 0x00FF00FFu; a12 = (c0y >> 8) & 0x00FF00FFu; a13 = (c1y >> 8) & 0x00FF00FFu;
+    } else {
+      a00 = q0.x & mask; a01 = q1.x & mask; a02 = (q0.x >> 8) & mask; a03 = (q1.x >> 8) & mask;
+      a10 = q0.y & mask; a11 = q1.y & mask; a12 = (q0.y >> 8) & mask; a13 = (q1.y >> 8) & mask;
+    }
 #pragma unroll
     for (int c = 0; c < NCG; c++) {
       const uint4 xq = cur.xq[c];
@@ -269,7 +287,8 @@ gemv_mma_q6k_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bflo
 #pragma unroll
     for (int i = 0; i < 4; i++) acc[cg][i] = 0.f;
 
-  // the loads of superblock b + 1 are issued before superblock b is multiplied
+  // the loads of superblock b + 1 are issued before superblock b is multiplied (a deeper register
+  // pipeline measured slower: the registers it takes cost more occupancy than the latency it hides)
   struct Raw { uint32_t d[2], sc[2], ql[2][2], qh[2][2]; uint2 xa[NCG], xb[NCG]; };
   auto load = [&](int b) {
     Raw r;
@@ -376,11 +395,14 @@ bool gemv_mma_applicable(const TypeInfo* ti, int64_t N, int64_t K, int M) {
 
 cudaError_t gemv_mma(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y,
                      int y_dtype, const uint8_t* tab, cudaStream_t st) {
-  if (ti->qtype == QT_Q4_K && K % 256 == 0 && (uintptr_t)w % 16 == 0) {
+  if ((ti->qtype == QT_Q4_K || ti->qtype == QT_Q5_K) && K % 256 == 0 && (uintptr_t)w % 16 == 0) {
     const unsigned grid = (unsigned)((N + 15) / 16);
     const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
-    if (M <= 8) mmav::gemv_mma_q4k_kernel<1><<<grid, mmav::kThreads, 0, st>>>(w, (int)N, (int)K, xb, M, y, y_dtype);
-    else mmav::gemv_mma_q4k_kernel<2><<<grid, mmav::kThreads, 0, st>>>(w, (int)N, (int)K, xb, M, y, y_dtype);
+    const bool q5 = ti->qtype == QT_Q5_K;
+    if (M <= 8 && !q5) mmav::gemv_mma_q45k_kernel<1, false><<<grid, mmav::kThreads, 0, st>>>(w, (int)N, (int)K, xb, M, y, y_dtype);
+    else if (!q5) mmav::gemv_mma_q45k_kernel<2, false><<<grid, mmav::kThreads, 0, st>>>(w, (int)N, (int)K, xb, M, y, y_dtype);
+    else if (M <= 8) mmav::gemv_mma_q45k_kernel<1, true><<<grid, mmav::kThreads, 0, st>>>(w, (int)N, (int)K, xb, M, y, y_dtype);
+    else mmav::gemv_mma_q45k_kernel<2, true><<<grid, mmav::kThreads, 0, st>>>(w, (int)N, (int)K, xb, M, y, y_dtype);
     return cudaPeekAtLastError();
   }
   if (ti->qtype == QT_Q6_K && K % 256 == 0 && (uintptr_t)w % 2 == 0) {

@@ -89,10 +89,13 @@ __device__ __forceinline__ float int8_to_float(uint32_t v_flipped) {
 }
 __device__ __forceinline__ int owner_of(int64_t u, int64_t U, int G) { return (int)(((u + 1) * G - 1) / U); }
 
-// Eight bytes of a block field at shared address a.  ODD: a = 2 (mod 4).
-template <bool ODD>
+// Eight bytes of a block field at shared address a.  ALIGN: 8 (one 64-bit load, conflict free at
+// this pitch), 4 (two words) or 2 (a = 2 mod 4: three aligned words and two funnel shifts).
+template <int ALIGN>
 __device__ __forceinline__ uint2 ld_field(uint32_t a) {
-  if constexpr (!ODD) {
+  if constexpr (ALIGN == 8) {
+    return *reinterpret_cast<const uint2*>(__cvta_shared_to_generic(a));
+  } else if constexpr (ALIGN == 4) {
     return make_uint2(lds32(a), lds32(a + 4));
   } else {
     const uint32_t w0 = lds32(a - 2), w1 = lds32(a + 2), w2 = lds32(a + 6);
@@ -109,7 +112,7 @@ struct LaneX {
 
 // Multiply one tile (16 rows x one superblock at `blk`, the block's first byte in the slot of row 0)
 // by its activations and add this lane's share of the row sums to out0 (row g) / out1 (row g + 8).
-template <bool ODD>
+template <int ALIGN>
 __device__ __forceinline__ void compute_tile(uint32_t blk, int g, int t, const LaneX& lx, uint32_t xsa, float f_hi,
                                              float& out0, float& out1) {
   const uint32_t b0 = blk + g * kSlotPitch, b1 = b0 + 8 * kSlotPitch;
@@ -117,10 +120,10 @@ __device__ __forceinline__ void compute_tile(uint32_t blk, int g, int t, const L
   const float d1 = __half2float(__ushort_as_half((unsigned short)lds16(b1 + 208)));
 #pragma unroll
   for (int h = 0; h < 2; h++) {
-    const uint2 qa0 = ld_field<ODD>(b0 + 64 * h + 8 * t), qb0 = ld_field<ODD>(b0 + 64 * h + 32 + 8 * t);
-    const uint2 qh0 = ld_field<ODD>(b0 + 128 + 32 * h + 8 * t);
-    const uint2 qa1 = ld_field<ODD>(b1 + 64 * h + 8 * t), qb1 = ld_field<ODD>(b1 + 64 * h + 32 + 8 * t);
-    const uint2 qh1 = ld_field<ODD>(b1 + 128 + 32 * h + 8 * t);
+    const uint2 qa0 = ld_field<ALIGN>(b0 + 64 * h + 8 * t), qb0 = ld_field<ALIGN>(b0 + 64 * h + 32 + 8 * t);
+    const uint2 qh0 = ld_field<ALIGN>(b0 + 128 + 32 * h + 8 * t);
+    const uint2 qa1 = ld_field<ALIGN>(b1 + 64 * h + 8 * t), qb1 = ld_field<ALIGN>(b1 + 64 * h + 32 + 8 * t);
+    const uint2 qh1 = ld_field<ALIGN>(b1 + 128 + 32 * h + 8 * t);
     uint4 xb[4];
 #pragma unroll
     for (int c = 0; c < 4; c++) xb[c] = lds128(lx.addr[c] + h * (lx.stride[c] >> 1));
@@ -332,8 +335,9 @@ gemv_q6k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
       cp_async_wait<DEPTH - 1>();
       __syncwarp();
       const uint32_t blk = my_ring + slot * kSlotBytes + skew;
-      if (odd) compute_tile<true>(blk, g, t, cur, xsa, f_hi, out0, out1);
-      else compute_tile<false>(blk, g, t, cur, xsa, f_hi, out0, out1);
+      if (odd) compute_tile<2>(blk, g, t, cur, xsa, f_hi, out0, out1);
+      else if (skew & 4) compute_tile<4>(blk, g, t, cur, xsa, f_hi, out0, out1);
+      else compute_tile<8>(blk, g, t, cur, xsa, f_hi, out0, out1);
       __syncwarp();
       if (++slot == DEPTH) slot = 0;
 #pragma unroll

@@ -96,7 +96,12 @@ size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32_t M);
  * scales), accumulation is float32, the only rounding to a narrow type is the output.
  * Replaces matmul_q4_k / matmul_q5_k / matmul_q6_k / matmul_iq4_xs / matmul_lowbit
  * (src/gguf_jax/cute/q4_k.py:282-329, q5_k.py:150-179, q6_k.py:115-144,
- * iq4_xs.py:146-175, lowbit.py:675-712). */
+ * iq4_xs.py:146-175, lowbit.py:675-712).
+ * The batch-1 kernels for Q4_K, Q5_K and Q6_K are launched as programmatic dependents: they may
+ * begin to read `w` (only `w`) while the previous launch of this library on the same stream is
+ * still finishing.  So `w` must not be an output of that previous launch; x, y and the
+ * workspace carry no such restriction.  The weight buffer must extend to the next 16-byte
+ * boundary (true of any device allocation). */
 int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
                  int32_t M, void* y, int32_t y_dtype, void* workspace,
                  size_t workspace_bytes, void* stream);
