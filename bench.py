@@ -248,10 +248,29 @@ def decode_leg(world: int, rank: int, dev) -> dict:
             h = layer_step(h, layers[li % DECODE_DISTINCT])
         return mm(h, head)
 
+    import ctypes
+
+    from gguf_jax_b200 import _lib
+
+    def device_status() -> int:
+        word = ctypes.c_int32(0)
+        _lib.lib().ggq_read_status(dev.index, ctypes.byref(word))
+        return int(word.value)
+
     stream = torch.cuda.Stream(dev)
     with torch.cuda.stream(stream):
+        t0 = time.perf_counter()
         logits = token()
         stream.synchronize()
+        eager_s = time.perf_counter() - t0
+        # a bounded wait that ran out (a peer's words never arrived) shows here: do not go on to
+        # replay hundreds of launches that would each sit out their wait limit
+        bad = torch.tensor([1 if (device_status() != 0 or eager_s > 20.0) else 0], device=dev)
+        if world > 1:
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()):
+            raise RuntimeError(f"decode chain gave up after its first token: device status {device_status()}, "
+                               f"{eager_s:.1f} s for one eager token")
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             logits = token()
@@ -282,15 +301,10 @@ def decode_leg(world: int, rank: int, dev) -> dict:
     finite = bool(torch.isfinite(lv).all())
     wbytes = sum(n * (k // 256) * _BLOCK_BYTES[q] for _, q, n, k in DECODE_LAYER) * DECODE_LAYERS
     wbytes += DECODE_HEAD[2] * (DECODE_HEAD[3] // 256) * _BLOCK_BYTES[DECODE_HEAD[1]]
-    import ctypes
-
-    from gguf_jax_b200 import _lib
-    word = ctypes.c_int32(0)
-    _lib.lib().ggq_read_status(dev.index, ctypes.byref(word))
     del graph
     return {"tok_s": 1e3 / ms, "ms_per_token": ms, "batch": 1, "launches_per_token": launches,
             "weight_gb_per_token": wbytes / 1e9, "aggregate_hbm_gbs": wbytes / (ms * 1e-3) / 1e9,
-            "logits_finite": finite, "logits_rms": float(lv.pow(2).mean().sqrt()), "device_status": int(word.value),
+            "logits_finite": finite, "logits_rms": float(lv.pow(2).mean().sqrt()), "device_status": device_status(),
             "exchange": "tagged words stored into every rank's buffer by the kernels (ggq_gemv_sharded_tagged)" if world > 1 else "none",
             "model": "Llama-3-70B-shaped Q4_K_M (attn_v, ffn_down, lm_head in Q6_K), GEMVs only, chained",
             "note": f"{DECODE_LAYERS} layer steps cycle over {DECODE_DISTINCT} distinct synthetic layer weight sets "

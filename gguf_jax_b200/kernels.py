@@ -28,6 +28,16 @@ __all__ = [
 LOWBIT_TYPES = (QT.Q2_K, QT.IQ1_S, QT.IQ1_M, QT.IQ2_XXS, QT.IQ2_XS, QT.IQ2_S, QT.IQ3_XXS, QT.IQ3_S)
 
 
+_ws_need: dict[tuple[int, int, int, int], int] = {}
+_cap: list[int] = []
+
+
+def _gemv_cap(L) -> int:
+    if not _cap:
+        _cap.append(int(L.ggq_gemv_max_batch()))
+    return _cap[0]
+
+
 def gemv_max_batch() -> int:
     """Largest flattened batch served by the small-batch kernel (``ggq_gemv``)."""
     return int(_lib.lib().ggq_gemv_max_batch())
@@ -64,13 +74,25 @@ def fused_matmul(x: torch.Tensor, w: QuantizedArray, *, out_dtype=torch.bfloat16
     y = torch.empty((m, n_rows), dtype=out_dtype, device=x.device)
     if m == 0:
         return y.reshape(*x.shape[:-1], n_rows)
-    fn = L.ggq_gemv if m <= L.ggq_gemv_max_batch() else L.ggq_gemm
-    with torch.cuda.device(dev):
-        need = L.ggq_workspace_bytes(int(w.qtype), n_rows, k_dim, m)
+    fn = L.ggq_gemv if m <= _gemv_cap(L) else L.ggq_gemm
+    # the common case (the tensors live on the current device) skips the device switch, which
+    # costs more host time than the rest of this function
+    switch = torch.cuda.current_device() != dev
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
+        key = (int(w.qtype), n_rows, k_dim, m)
+        need = _ws_need.get(key)
+        if need is None:
+            need = _ws_need[key] = L.ggq_workspace_bytes(*key)
         ws = _backend.workspace(dev, need)
-        _lib.check(fn(int(w.qtype), data.data_ptr(), n_rows, k_dim, xm.data_ptr(), m, y.data_ptr(),
+        _lib.check(fn(key[0], data.data_ptr(), n_rows, k_dim, xm.data_ptr(), m, y.data_ptr(),
                       _backend.dtype_code(out_dtype), ws.data_ptr() if ws is not None else None,
                       ws.numel() if ws is not None else 0, _backend.stream_ptr(dev)))
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
     return y.reshape(*x.shape[:-1], n_rows)
 
 
