@@ -393,8 +393,10 @@ def run_ours(args) -> None:
             if rank == 0:
                 print(f"[bench] {exchange}: {e}", file=sys.stderr)
 
+    use_peer = [peer is not None]
+
     def step(i: int):
-        if peer is not None:
+        if use_peer[0]:
             y = peer.matmul(x, weights[i % copies], wait_previous=True)
         else:
             y = kernels.fused_matmul(x, weights[i % copies])
@@ -419,6 +421,20 @@ def run_ours(args) -> None:
         for i in range(max(args.warmup, 3)):
             step(i)
         stream.synchronize()
+        if world > 1 and use_peer[0]:
+            # a flag wait that ran out during the warm-up means the peers' stores do not arrive:
+            # fall back to the NCCL route rather than sit out the wait limit on every step
+            import ctypes
+            word = ctypes.c_int32(0)
+            _lib.lib().ggq_read_status(dev.index, ctypes.byref(word))
+            bad = torch.tensor([1 if word.value else 0], device=dev)
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+            if int(bad.item()):
+                use_peer[0] = False
+                exchange = "NCCL all-gather (the fused exchange's bounded wait expired during warm-up)"
+                for i in range(3):
+                    step(i)
+                stream.synchronize()
         # one CUDA graph of `steps` launches: the Python/ctypes launch cost would otherwise
         # exceed the ~20 us kernel
         graph = None
@@ -485,7 +501,7 @@ def run_ours(args) -> None:
 
     def e2e_step(i: int):
         xd = xh.to(dev, non_blocking=True)
-        if peer is not None:
+        if use_peer[0]:
             y = peer.matmul(xd, weights[i % copies], wait_previous=True)
             torch.cuda.current_stream().synchronize()
             dist.barrier()              # every rank's rows have landed before the host reads them
