@@ -54,7 +54,8 @@ namespace q4k {
 constexpr int kBlockBytes = 144;
 constexpr int kRowTiles = 2;                   // 16-row tiles per unit
 constexpr int kWarps = 8 * kRowTiles;          // one warp per (row tile, superblock pair of the chunk)
-constexpr int kThreads = kWarps * 32;
+constexpr int kThreads = (kWarps + 1) * 32;    // sixteen tile warps and one reducer warp
+constexpr int kBarFull = 1, kBarFree = 3;      // named barriers (two each, alternating) of the flush hand-off
 constexpr int kRowsPerUnit = 16 * kRowTiles;
 constexpr int kSbPerWarp = 2;                  // adjacent superblocks a warp multiplies per step
 constexpr int kSbPerUnit = 8 * kSbPerWarp;
@@ -84,6 +85,8 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 __device__ __forceinline__ void cp_async16(uint32_t dst, const uint8_t* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
+__device__ __forceinline__ void bar_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+__device__ __forceinline__ void bar_arrive(int id, int count) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -254,8 +257,11 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
     cp_async_commit();
   };
   // Fill the pipeline before the activation prologue so HBM is busy from the first cycle.
+  const bool tile_warp = warp < kWarps;           // the last warp only reduces and publishes row sums
+  if (tile_warp) {
 #pragma unroll
-  for (int d = 0; d < DEPTH - 1; d++) issue_next();
+    for (int d = 0; d < DEPTH - 1; d++) issue_next();
+  }
 
   float* xs = reinterpret_cast<float*>(smem + L.xs(K));
   int* xmax = reinterpret_cast<int*>(smem + L.misc(K));
@@ -341,44 +347,62 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
 
   auto emit = [&](int row, float v) { peer_emit(pp, y, y_dtype, row, v, out_tag); };
 
-  // ---- multiply side: walk my units row group by row group ----
-  int rg = rg_begin, c = c_begin, done = 0, slot = 0, flush_parity = 0;
-  while (done < n_units) {
-    const int c_first = c;
-    const int c_stop = min(C, c + (n_units - done));     // chunks [c, c_stop) of row group rg are mine
-    float out0 = 0.f, out1 = 0.f;                        // rows g and g+8 of this warp's tile, this lane's share
-    int sbg = c * kSbPerUnit + kSbPerWarp * j;
-    uint32_t xa = x_lane_base + (uint32_t)sbg * x_sb_stride;
-    uint32_t xsa = xs_lane_base + (uint32_t)sbg * 32u;
-    for (; c < c_stop; ++c) {
-      issue_next();                                      // keeps DEPTH - 1 steps in flight
-      cp_async_wait<DEPTH - 1>();                        // the oldest one has landed
-      __syncwarp();
-      const uint32_t tile = my_ring + slot * kSlotBytes;
-      if (sbg < SB) compute_tile(tile, g, t, lc, xa, x_step, xsa, out0, out1);
-      if constexpr (kSbPerWarp == 2) {
-        if (sbg + 1 < SB) compute_tile(tile + kBlockBytes, g, t, lc, xa + x_sb_stride, x_step, xsa + 32u, out0, out1);
+  // ---- multiply side: the tile warps walk the CTA's units row group by row group; at the end of a
+  // row group they leave their row sums in shared memory and go on, and the reducer warp folds
+  // them, settles split row groups with the other CTAs and stores the outputs.  The hand-off is
+  // two pairs of named barriers (buffer full / buffer free), so a tile warp never waits for the
+  // global-memory round trips of the reduction and the reducer never delays a tile.
+  if (tile_warp) {
+    int rg = rg_begin, c = c_begin, done = 0, slot = 0, flush_i = 0;
+    while (done < n_units) {
+      const int c_first = c;
+      const int c_stop = min(C, c + (n_units - done));     // chunks [c, c_stop) of row group rg are mine
+      float out0 = 0.f, out1 = 0.f;                        // rows g and g+8 of this warp's tile, this lane's share
+      int sbg = c * kSbPerUnit + kSbPerWarp * j;
+      uint32_t xa = x_lane_base + (uint32_t)sbg * x_sb_stride;
+      uint32_t xsa = xs_lane_base + (uint32_t)sbg * 32u;
+      for (; c < c_stop; ++c) {
+        issue_next();                                      // keeps DEPTH - 1 steps in flight
+        cp_async_wait<DEPTH - 1>();                        // the oldest one has landed
+        __syncwarp();
+        const uint32_t tile = my_ring + slot * kSlotBytes;
+        if (sbg < SB) compute_tile(tile, g, t, lc, xa, x_step, xsa, out0, out1);
+        if constexpr (kSbPerWarp == 2) {
+          if (sbg + 1 < SB) compute_tile(tile + kBlockBytes, g, t, lc, xa + x_sb_stride, x_step, xsa + 32u, out0, out1);
+        }
+        __syncwarp();   // every lane is done with the slot before a later copy overwrites it
+        if (++slot == DEPTH) slot = 0;
+        sbg += kSbPerUnit;
+        xa += kSbPerUnit * x_sb_stride;
+        xsa += kSbPerUnit * 32u;
       }
-      __syncwarp();   // every lane is done with the slot before a later copy overwrites it
-      if (++slot == DEPTH) slot = 0;
-      sbg += kSbPerUnit;
-      xa += kSbPerUnit * x_sb_stride;
-      xsa += kSbPerUnit * 32u;
+      done += c_stop - c_first;
+      // fold the four lanes of a quad, then hand the 16 row sums of this warp to the reducer
+      float v0 = out0, v1 = out1;
+      v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, 1); v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, 2);
+      v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 1); v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 2);
+      const int p = flush_i & 1;
+      if (flush_i >= 2) bar_sync(kBarFree + p, kThreads);  // the reducer has read this buffer's previous content
+      float* redbuf = red + p * (kWarps * 16);
+      if (t == 0) {
+        redbuf[warp * 16 + g] = v0 * d_up;      // undo the power-of-two scaling of the activations
+        redbuf[warp * 16 + g + 8] = v1 * d_up;
+      }
+      __threadfence_block();
+      bar_arrive(kBarFull + p, kThreads);
+      ++flush_i;
+      if (c == C) { c = 0; ++rg; }
     }
-    done += c_stop - c_first;
-
-    // ---- flush the row group: fold lanes, fold the warps that shared a row tile, publish ----
-    float v0 = out0, v1 = out1;
-    v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, 1); v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, 2);
-    v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 1); v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 2);
-    float* redbuf = red + flush_parity * (kWarps * 16);
-    if (t == 0) {
-      redbuf[warp * 16 + g] = v0 * d_up;      // undo the power-of-two scaling of the activations
-      redbuf[warp * 16 + g + 8] = v1 * d_up;
-    }
-    flush_parity ^= 1;
-    __syncthreads();
-    if (warp == 0) {
+  } else {
+    int rg = rg_begin, c = c_begin, done = 0, flush_i = 0;
+    while (done < n_units) {
+      const int c_first = c;
+      const int c_stop = min(C, c + (n_units - done));
+      done += c_stop - c_first;
+      c = c_stop;
+      const int p = flush_i & 1;
+      bar_sync(kBarFull + p, kThreads);                    // all sixteen tile warps have written their sums
+      const float* redbuf = red + p * (kWarps * 16);
       const bool complete = (c_first == 0) && (c_stop == C);
       const int64_t rg_first_unit = (int64_t)rg * C, rg_last_unit = rg_first_unit + C - 1;
       float v[2];
@@ -391,6 +415,9 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
           for (int jj = 0; jj < 8; jj++) v[h] += redbuf[((r >> 4) * 8 + jj) * 16 + (r & 15)];
         }
       }
+      __syncwarp();
+      bar_arrive(kBarFree + p, kThreads);                  // the buffer may be overwritten
+      ++flush_i;
       if (complete) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
@@ -423,8 +450,8 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
           if (lane == 0) counters[rg] = 0;
         }
       }
+      if (c == C) { c = 0; ++rg; }
     }
-    if (c == C) { c = 0; ++rg; }
   }
   cp_async_wait<0>();
   peer_publish(pp, tid, G);
