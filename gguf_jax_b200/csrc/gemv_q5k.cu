@@ -23,7 +23,8 @@ namespace q5k {
 constexpr int kBlockBytes = 176;
 constexpr int kRowTiles = 2;                   // 16-row tiles per unit
 constexpr int kWarps = 8 * kRowTiles;
-constexpr int kThreads = kWarps * 32;
+constexpr int kThreads = (kWarps + 1) * 32;    // sixteen tile warps and one reducer warp
+constexpr int kBarFull = 1, kBarFree = 3;      // named barriers (two each, alternating) of the flush hand-off
 constexpr int kRowsPerUnit = 16 * kRowTiles;
 constexpr int kSbPerUnit = 8;                  // one superblock per warp and step
 constexpr int kPieces = 11;                    // 16-byte pieces per row and step
@@ -49,6 +50,8 @@ __device__ __forceinline__ uint32_t lds16(uint32_t a) { return *reinterpret_cast
 __device__ __forceinline__ void cp_async16(uint32_t dst, const uint8_t* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
+__device__ __forceinline__ void bar_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+__device__ __forceinline__ void bar_arrive(int id, int count) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -204,8 +207,11 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
     }
     cp_async_commit();
   };
+  const bool tile_warp = warp < kWarps;           // the last warp only reduces and publishes row sums
+  if (tile_warp) {
 #pragma unroll
-  for (int d = 0; d < DEPTH - 1; d++) issue_next();
+    for (int d = 0; d < DEPTH - 1; d++) issue_next();
+  }
 
   float* xs = reinterpret_cast<float*>(smem + L.xs(K));
   int* xmax = reinterpret_cast<int*>(smem + L.misc(K));
@@ -284,45 +290,65 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
   const float f_lo = 16.f / (float)(1 << (2 * t)), f_hi = 128.f / (float)(1 << (2 * t));
   float* red = reinterpret_cast<float*>(smem + L.red(K));
 
-  int rg = rg_begin, c = c_begin, done = 0, slot = 0, flush_parity = 0;
-  while (done < n_units) {
-    const int c_first = c;
-    const int c_stop = min(C, c + (n_units - done));
-    float out0 = 0.f, out1 = 0.f;
-    int sbg = c * kSbPerUnit + j;
-    uint32_t xa = x_lane_base + (uint32_t)sbg * x_sb_stride;
-    uint32_t xsa = xs_lane_base + (uint32_t)sbg * 32u;
-    for (; c < c_stop; ++c) {
-      issue_next();
-      cp_async_wait<DEPTH - 1>();
-      __syncwarp();
-      if (sbg < SB) compute_tile(my_ring + slot * kSlotBytes, g, t, lc, m1, f_lo, f_hi, xa, x_step, xsa, out0, out1);
-      __syncwarp();
-      if (++slot == DEPTH) slot = 0;
-      sbg += kSbPerUnit;
-      xa += kSbPerUnit * x_sb_stride;
-      xsa += kSbPerUnit * 32u;
-    }
-    done += c_stop - c_first;
+  // The tile warps leave their row sums in shared memory at the end of a row group and go on; the
+  // reducer warp folds them, settles split row groups with the other CTAs and stores the outputs
+  // (hand-off through two pairs of named barriers, as in gemv_q4k.cu).
+  if (tile_warp) {
+    int rg = rg_begin, c = c_begin, done = 0, slot = 0, flush_i = 0;
+    while (done < n_units) {
+      const int c_first = c;
+      const int c_stop = min(C, c + (n_units - done));
+      float out0 = 0.f, out1 = 0.f;
+      int sbg = c * kSbPerUnit + j;
+      uint32_t xa = x_lane_base + (uint32_t)sbg * x_sb_stride;
+      uint32_t xsa = xs_lane_base + (uint32_t)sbg * 32u;
+      for (; c < c_stop; ++c) {
+        issue_next();
+        cp_async_wait<DEPTH - 1>();
+        __syncwarp();
+        if (sbg < SB) compute_tile(my_ring + slot * kSlotBytes, g, t, lc, m1, f_lo, f_hi, xa, x_step, xsa, out0, out1);
+        __syncwarp();
+        if (++slot == DEPTH) slot = 0;
+        sbg += kSbPerUnit;
+        xa += kSbPerUnit * x_sb_stride;
+        xsa += kSbPerUnit * 32u;
+      }
+      done += c_stop - c_first;
 
-    // ---- flush the row group ----
-    float v0 = out0, v1 = out1;
-    v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, 1); v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, 2);
-    v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 1); v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 2);
-    float* redbuf = red + flush_parity * (kWarps * 16);
-    if (t == 0) {
-      redbuf[warp * 16 + g] = v0 * d_up;
-      redbuf[warp * 16 + g + 8] = v1 * d_up;
+      float v0 = out0, v1 = out1;
+      v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, 1); v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, 2);
+      v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 1); v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 2);
+      const int p = flush_i & 1;
+      if (flush_i >= 2) bar_sync(kBarFree + p, kThreads);  // the reducer has read this buffer's previous content
+      float* redbuf = red + p * (kWarps * 16);
+      if (t == 0) {
+        redbuf[warp * 16 + g] = v0 * d_up;
+        redbuf[warp * 16 + g + 8] = v1 * d_up;
+      }
+      __threadfence_block();
+      bar_arrive(kBarFull + p, kThreads);
+      ++flush_i;
+      if (c == C) { c = 0; ++rg; }
     }
-    flush_parity ^= 1;
-    __syncthreads();
-    if (warp == 0) {
+  } else {
+    int rg = rg_begin, c = c_begin, done = 0, flush_i = 0;
+    while (done < n_units) {
+      const int c_first = c;
+      const int c_stop = min(C, c + (n_units - done));
+      done += c_stop - c_first;
+      c = c_stop;
+      const int p = flush_i & 1;
+      bar_sync(kBarFull + p, kThreads);                    // all sixteen tile warps have written their sums
+      const float* redbuf = red + p * (kWarps * 16);
       const bool complete = (c_first == 0) && (c_stop == C);
       const int64_t rg_first_unit = (int64_t)rg * C, rg_last_unit = rg_first_unit + C - 1;
       const int r = lane;                         // row within the unit
       float v = 0.f;
 #pragma unroll
       for (int jj = 0; jj < 8; jj++) v += redbuf[((r >> 4) * 8 + jj) * 16 + (r & 15)];
+      __syncwarp();
+      bar_arrive(kBarFree + p, kThreads);                  // the buffer may be overwritten
+      ++flush_i;
       const int row = rg * kRowsPerUnit + r;
       if (complete) {
         if (row < N) peer_emit(pp, y, y_dtype, row, v, out_tag);
@@ -347,8 +373,8 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
           if (lane == 0) counters[rg] = 0;
         }
       }
+      if (c == C) { c = 0; ++rg; }
     }
-    if (c == C) { c = 0; ++rg; }
   }
   cp_async_wait<0>();
   peer_publish(pp, tid, G);
