@@ -54,7 +54,7 @@ UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from
 # the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 137_200_000
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 136_000_000
 NCU_TRAFFIC_SOURCE = "profiles/q4k_gemv_m1_8192x28672.md (dram__bytes_read.sum + dram__bytes_write.sum, ncu --set full, 1 GPU, full weight)"
 
 
