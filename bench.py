@@ -386,18 +386,23 @@ def run_ours(args) -> None:
     exchange = "none"
     if world > 1:
         try:
-            peer = sharded.PeerOutput(None, max_batch=BATCH, n_total=N_ROWS, device=dev)
-            exchange = "fused peer-store epilogue + flags (ggq_gemv_sharded)"
+            peer = sharded.TaggedExchange(None, n_max=N_ROWS, device=dev,
+                                          n_buffers=sharded.TaggedExchange.buffers_for(args.steps, max_back=1))
+            exchange = ("tagged words stored into every rank's buffer by the kernel; each launch waits until the "
+                        "previous exchange has landed (ggq_gemv_sharded_tagged)")
         except Exception as e:  # noqa: BLE001
             exchange = f"NCCL all-gather (symmetric memory unavailable: {type(e).__name__})"
             if rank == 0:
                 print(f"[bench] {exchange}: {e}", file=sys.stderr)
+    prev = [None]          # the previous step's result: the next launch is ordered after it
+    seam = [False]         # first launch of a captured graph: its predecessor is not in the graph
 
     use_peer = [peer is not None]
 
     def step(i: int):
         if use_peer[0]:
-            y = peer.matmul(x, weights[i % copies], wait_previous=True)
+            y = peer.matmul(x, weights[i % copies], after=None if (seam[0] and i == 0) else prev[0])
+            prev[0] = y
         else:
             y = kernels.fused_matmul(x, weights[i % copies])
             if world > 1:
@@ -440,9 +445,11 @@ def run_ours(args) -> None:
         graph = None
         try:
             graph = torch.cuda.CUDAGraph()
+            seam[0] = True
             with torch.cuda.graph(graph, stream=stream):
                 for i in range(args.steps):
                     step(i)
+            seam[0] = False
         except Exception as e:  # noqa: BLE001
             graph = None
             if rank == 0:
@@ -502,10 +509,10 @@ def run_ours(args) -> None:
     def e2e_step(i: int):
         xd = xh.to(dev, non_blocking=True)
         if use_peer[0]:
-            y = peer.matmul(xd, weights[i % copies], wait_previous=True)
+            y = peer.matmul(xd.reshape(-1), weights[i % copies])
             torch.cuda.current_stream().synchronize()
             dist.barrier()              # every rank's rows have landed before the host reads them
-            yh.copy_(y, non_blocking=True)
+            yh.copy_(y.to_tensor(), non_blocking=True)
         elif world > 1:
             y = gj.matmul(xd, weights[i % copies])
             dist.all_gather_into_tensor(y_full, y)

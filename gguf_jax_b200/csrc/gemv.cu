@@ -149,6 +149,7 @@ extern "C" int32_t ggq_gemv_sharded(int32_t qtype, const void* w, int64_t N_loca
 
 extern "C" int32_t ggq_gemv_sharded_tagged(int32_t qtype, const void* w, int64_t N_local, int64_t K,
                                            const void* x_bf16, const uint32_t* x_tagged, int32_t x_back,
+                                           const uint32_t* after_tagged, int64_t after_words, int32_t after_back,
                                            uint32_t* const* y_peers, uint32_t* state, int32_t world, int32_t rank,
                                            int64_t n_total, void* workspace, size_t workspace_bytes, void* stream) {
   const TypeInfo* ti = type_info(qtype);
@@ -162,6 +163,10 @@ extern "C" int32_t ggq_gemv_sharded_tagged(int32_t qtype, const void* w, int64_t
     return fail(GGQ_MISALIGNED, "ggq_gemv_sharded_tagged: null pointer (give exactly one of x_bf16, x_tagged)");
   if (x_tagged && (x_back < 1 || x_back > 65534))
     return fail(GGQ_BAD_SHAPE, "ggq_gemv_sharded_tagged: x_back=%d", x_back);
+  if (after_tagged && (after_back < 1 || after_back > 65534 || after_words < 0 || after_words % 4 ||
+                       (uintptr_t)after_tagged % 16))
+    return fail(GGQ_BAD_SHAPE, "ggq_gemv_sharded_tagged: after_back=%d after_words=%lld (a multiple of 4, 16-byte "
+                "aligned)", after_back, (long long)after_words);
   const void* xa = x_bf16 ? x_bf16 : (const void*)x_tagged;
   const bool ok4 = qtype == QT_Q4_K && gemv_q4k_applicable(N_local, K, 1, w, xa);
   const bool ok5 = qtype == QT_Q5_K && gemv_q5k_applicable(N_local, K, 1, w, xa);
@@ -187,6 +192,9 @@ extern "C" int32_t ggq_gemv_sharded_tagged(int32_t qtype, const void* w, int64_t
   pp.tagged = 1;
   pp.x_tagged = x_tagged;
   pp.x_back = x_tagged ? x_back : 1;
+  pp.after_tagged = after_tagged;
+  pp.after_words = after_tagged ? after_words : 0;
+  pp.after_back = after_tagged ? after_back : 1;
   cudaError_t (*kernel)(const uint8_t*, int64_t, int64_t, const void*, void*, int, void*, size_t, int, int*,
                         cudaStream_t, const PeerPublish*) = ok4 ? gemv_q4k : ok5 ? gemv_q5k : gemv_q6k;
   cudaError_t err = kernel((const uint8_t*)w, N_local, K, xa, nullptr, GGQ_BF16, workspace, workspace_bytes,

@@ -45,6 +45,11 @@ struct PeerPublish {
   int tagged;                     // 1: emit tagged words, do not raise flags
   const uint32_t* x_tagged;       // activations as tagged words of an earlier exchange (nullptr: plain bf16 x)
   int x_back;                     // that exchange was the x_back-th most recent one (1 = the previous launch)
+  // Optional: do not start before an earlier exchange has landed completely in this rank's buffer
+  // (the ordering the flag protocol gives, without its fences): every CTA polls these words.
+  const uint32_t* after_tagged;   // nullptr: no such wait
+  int64_t after_words;
+  int after_back;
   // Each flag array has world + 2 words: [0, world) are raised by the peers; word `world` is this
   // rank's epoch (number of exchanges it has published), word world + 1 counts finished CTAs of
   // the running launch.  All ranks issue the same sequence of sharded launches, so "the previous
@@ -128,6 +133,26 @@ __device__ __forceinline__ uint4 peer_load8_tagged(const uint32_t* xt, int idx8,
   // word pairs (lo16 of even element | lo16 of odd element << 16)
   return make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410),
                     __byte_perm(b.x, b.y, 0x5410), __byte_perm(b.z, b.w, 0x5410));
+}
+
+// Wait (bounded, like peer_load8_tagged) until all `words` tagged words at `v` carry tag_hi.
+// `words` is a multiple of 4 and `v` 16-byte aligned.
+__device__ __forceinline__ void peer_wait_tagged(const uint32_t* v, int64_t words, uint32_t tag_hi, int tid, int n_threads,
+                                                 int* status) {
+  for (int64_t i = 4 * (int64_t)tid; i < words; i += 4 * (int64_t)n_threads) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; it++) {
+      uint4 a;
+      asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(v + i) : "memory");
+      if (!(((a.x ^ tag_hi) | (a.y ^ tag_hi) | (a.z ^ tag_hi) | (a.w ^ tag_hi)) >> 16)) break;
+      if ((it & 63) == 0) {
+        uint64_t t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (it == 0) t0 = t1;
+        else if (t1 - t0 > 50000000ull) { if (status) atomicOr(status, STATUS_WAIT_EXPIRED); break; }
+      }
+    }
+  }
 }
 
 // One output value: locally, or into every rank's copy of the full output when row-sharded.

@@ -226,6 +226,9 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
       const uint32_t e = pp.flags[pp.rank][pp.world];        // exchanges this rank has completed
       out_tag = peer_tag_of(e + 1) << 16;
       x_tag = peer_tag_of(e + 1 - (uint32_t)pp.x_back) << 16;
+      if (pp.after_tagged)
+        peer_wait_tagged(pp.after_tagged, pp.after_words, peer_tag_of(e + 1 - (uint32_t)pp.after_back) << 16, tid,
+                         kThreads, status);
     }
     __syncthreads();
     const uint4* xg = reinterpret_cast<const uint4*>(x);

@@ -210,9 +210,11 @@ class TaggedExchange:
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
 
-    def matmul(self, x, w_shard: QuantizedArray) -> TaggedVector:
+    def matmul(self, x, w_shard: QuantizedArray, after: TaggedVector | None = None) -> TaggedVector:
         """``x @ w.T`` for this rank's rows of ``w``; ``x`` is a bf16 tensor of ``K`` elements or the
-        :class:`TaggedVector` of an earlier launch (its first ``K`` words are used)."""
+        :class:`TaggedVector` of an earlier launch (its first ``K`` words are used).  ``after``
+        names an earlier result that must have landed completely on this rank before the kernel
+        reads its activations (what the flag protocol's ``wait_previous`` gives)."""
         k = w_shard.shape[1]
         n_out = w_shard.shape[0] * self.world
         if n_out > self.n_max:
@@ -235,13 +237,19 @@ class TaggedExchange:
                 raise ValueError(f"x must be {k} bfloat16 values, got {tuple(x.shape)} {x.dtype}")
             x = x.contiguous()
             x_plain = x.data_ptr()
+        after_ptr, after_words, after_back = None, 0, 0
+        if after is not None:
+            after_back = self._serial - after.serial + 1
+            if after.owner is not self or after_back < 1 or after_back > len(self._bufs) - 2:
+                raise ValueError("`after` must be a recent result of this exchange")
+            after_ptr, after_words = self._bufs[after.index].data_ptr(), after.n // 4 * 4
         self._serial += 1
         index = self._serial % len(self._bufs)
         with torch.cuda.device(dev):
             ws = _backend.workspace(dev, L.ggq_workspace_bytes(int(w_shard.qtype), w_shard.shape[0], k, 1))
             _lib.check(L.ggq_gemv_sharded_tagged(
                 int(w_shard.qtype), w_shard.data.data_ptr(), w_shard.shape[0], k, x_plain, x_tagged, back,
-                self._buf_ptrs[index], self._state.data_ptr(), self.world, self.rank, n_out,
+                after_ptr, after_words, after_back, self._buf_ptrs[index], self._state.data_ptr(), self.world, self.rank, n_out,
                 ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
                 _backend.stream_ptr(dev)))
         return TaggedVector(self, index, n_out, self._serial)

@@ -143,11 +143,15 @@ int32_t ggq_gemv_sharded(int32_t qtype, const void* w, int64_t N_local, int64_t 
  * the kernel then polls each word until its tag is the expected one (bounded: GGQ_TIMEOUT via
  * ggq_read_status).  `state` is this rank's array of (world + 2) uint32, zero-filled once, that
  * only this function touches: it counts the exchanges, from which both tags are derived on the
- * device, so a captured CUDA graph can be replayed.  All ranks must issue the same sequence of
- * calls; a buffer may be reused for a new exchange once x_back_max + 2 exchanges have passed. */
+ * device, so a captured CUDA graph can be replayed.  after_tagged (optional, may be NULL) names
+ * after_words tagged words of the exchange after_back launches ago in this rank's own buffer:
+ * the kernel does not read its activations before all of them have arrived, which orders it
+ * after that exchange the way ggq_gemv_sharded's flags would.  All ranks must issue the same
+ * sequence of calls; a buffer may be reused for a new exchange once x_back_max + 2 exchanges have passed. */
 int32_t ggq_gemv_sharded_tagged(int32_t qtype, const void* w, int64_t N_local, int64_t K,
                                 const void* x_bf16, const uint32_t* x_tagged, int32_t x_back,
-                                uint32_t* const* y_peers, uint32_t* state, int32_t world,
+                                const uint32_t* after_tagged, int64_t after_words,
+                                int32_t after_back, uint32_t* const* y_peers, uint32_t* state, int32_t world,
                                 int32_t rank, int64_t n_total, void* workspace,
                                 size_t workspace_bytes, void* stream);
 

@@ -76,7 +76,7 @@ def main():
         outs.append(ex.matmul(outs[0], shards[1]))
         outs.append(ex.matmul(outs[1], shards[2]))
         outs.append(ex.matmul(outs[1], shards[3]))      # consumes a result two launches old
-        outs.append(ex.matmul(outs[3], shards[4]))
+        outs.append(ex.matmul(outs[3], shards[4], after=outs[2]))   # and ordered after another result
         return outs
 
     def check_chain(outs, what):

@@ -67,13 +67,13 @@ def test_sharded_entry_points_validate_before_any_cuda_call(built_lib):
     assert built_lib.ggq_gemv_sharded(int(QT.Q4_K), None, 64, 256, None, 1, ptrs, ptrs, 2, 2, 128, 1, 0, None, 0, None) == 2
     # the shards do not fit the output
     assert built_lib.ggq_gemv_sharded(int(QT.Q4_K), None, 64, 256, None, 1, ptrs, ptrs, 2, 0, 100, 1, 0, None, 0, None) == 2
-    assert built_lib.ggq_gemv_sharded_tagged(int(QT.Q4_K), None, 64, 256, None, None, 1, ptrs, None, 9, 0, 576,
-                                             None, 0, None) == 2
-    assert built_lib.ggq_gemv_sharded_tagged(int(QT.I8), None, 64, 256, None, None, 1, ptrs, None, 2, 0, 128,
-                                             None, 0, None) == 1
+    assert built_lib.ggq_gemv_sharded_tagged(int(QT.Q4_K), None, 64, 256, None, None, 1, None, 0, 0, ptrs, None, 9, 0,
+                                             576, None, 0, None) == 2
+    assert built_lib.ggq_gemv_sharded_tagged(int(QT.I8), None, 64, 256, None, None, 1, None, 0, 0, ptrs, None, 2, 0,
+                                             128, None, 0, None) == 1
     # neither plain nor tagged activations
-    assert built_lib.ggq_gemv_sharded_tagged(int(QT.Q4_K), None, 64, 256, None, None, 1, ptrs, None, 2, 0, 128,
-                                             None, 0, None) == 3   # MISALIGNED (null pointer)
+    assert built_lib.ggq_gemv_sharded_tagged(int(QT.Q4_K), None, 64, 256, None, None, 1, None, 0, 0, ptrs, None, 2, 0,
+                                             128, None, 0, None) == 3   # MISALIGNED (null pointer)
     assert b"null pointer" in built_lib.ggq_last_error()
 
 
