@@ -296,14 +296,14 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
       // the same L2 lines in lockstep.
       const int n_sub = K / 32;
       const int rot = (int)(((int64_t)b * n_sub) / G) & ~1;      // even: keeps sub-block parity
-      for (int i = tid; i < n_sub; i += kThreads) {
-        int sblk = i + rot;
-        if (sblk >= n_sub) sblk -= n_sub;
-        const float up = (sblk & 1) ? up_odd : up_even;
-        uint4 v[4];
+      // two sub-blocks per thread and round, both loads issued before either is converted
+      auto fetch = [&](int sblk, uint4 (&v)[4]) {
 #pragma unroll
         for (int q = 0; q < 4; q++)
           v[q] = pp.x_tagged ? peer_load8_tagged(pp.x_tagged, sblk * 4 + q, x_tag, status) : __ldg(xg + sblk * 4 + q);
+      };
+      auto convert = [&](int sblk, const uint4 (&v)[4]) {
+        const float up = (sblk & 1) ? up_odd : up_even;
         float sum = 0.f, asum = 0.f;
 #pragma unroll
         for (int q = 0; q < 4; q++) {
@@ -321,6 +321,18 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
         }
         xs[sblk] = sum * xs_scale;
         amax = fmaxf(amax, asum);
+      
+      };
+      auto rotated = [&](int i) { int sblk = i + rot; return sblk >= n_sub ? sblk - n_sub : sblk; };
+      for (int i = tid; i < n_sub; i += 2 * kThreads) {
+        const int s0 = rotated(i), i1 = i + kThreads;
+        const bool two = i1 < n_sub;
+        const int s1 = two ? rotated(i1) : s0;
+        uint4 v0[4], v1[4];
+        fetch(s0, v0);
+        if (two) fetch(s1, v1);
+        convert(s0, v0);
+        if (two) convert(s1, v1);
       }
       return amax;
     };
