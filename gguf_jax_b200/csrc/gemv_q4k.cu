@@ -1,6 +1,7 @@
 // Q4_K fused decode + multiply for batch 1, tuned for B200 HBM bandwidth.
 //
-// Data movement.  A persistent CTA per SM with sixteen warps.  Every warp streams its own
+// Data movement.  A persistent CTA per SM with sixteen tile warps (and a seventeenth that only
+// reduces and publishes row sums, see the multiply side).  Every warp streams its own
 // steps (16 weight rows x two adjacent 144-byte superblocks, 4.6 KB) from HBM into a private
 // ring of shared-memory slots with 16-byte cp.async copies, one to three steps ahead of the
 // one it is multiplying (as many as shared memory allows next to the staged activations; no

@@ -24,7 +24,8 @@
 // tile collects all eight group sums of 16 rows and lane (g, t) ends up with the sums of rows
 // g, g+8 and groups 2t, 2t+1 -- whose two int8 scales are one 16-bit load.
 //
-// Data movement.  Persistent CTA per SM, sixteen warps, each streaming its own tiles (16 rows
+// Data movement.  Persistent CTA per SM, sixteen tile warps (plus a reducer warp, as in
+// gemv_q4k.cu), each streaming its own tiles (16 rows
 // x one superblock) into a private ring of shared-memory slots with 16-byte cp.async copies.
 // A 210-byte block is only 2-byte aligned, so a step copies the 16-byte aligned window of 224
 // bytes that contains the block and the multiply reads its fields at the block's offset in that
