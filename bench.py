@@ -73,7 +73,7 @@ def measured_peak():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons every 100 ms while the timed region runs."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -90,7 +90,7 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-i", str(self.gpu), "-lms", "200"],
+                 "-i", str(self.gpu), "-lms", "100"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:  # noqa: BLE001
             self.proc = None
@@ -124,30 +124,44 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_baseline(seconds: float = 10.0, rows: int = 1024) -> dict:
-    """The CPU restatement (oracle/, OpenMP, float32) on a bounded row sample."""
-    import numpy as np
+def cpu_product(min_seconds: float, min_passes: int, warmup: int) -> dict:
+    """Times the CPU restatement of the reference's route (dequantize + multiply, fused per row, float32,
+    oracle/, OpenMP) on the whole 8192 x 28672 weight of the headline workload with every host core.
+    Used by both the ``cpu_baseline`` key and ``--impl reference``, so the two always agree on code path,
+    sample and thread count.  The thread count is set explicitly: launchers such as torchrun export
+    OMP_NUM_THREADS=1 to their children."""
     from gguf.constants import GGMLQuantizationType as QT
 
     from gguf_jax_b200 import synth
     from oracle import oracle as O
 
+    cores = O.set_threads(os.cpu_count() or 1)
     qt = QT[QTYPE_NAME]
-    w = synth.make_weight_bytes(rows, K_DIM, qt, seed=0)
+    w = synth.make_weight_bytes(N_ROWS, K_DIM, qt, seed=0)
     x = O.bf16_bits(synth.make_x(BATCH, K_DIM, seed=0))
-    O.c_matmul(x, w[:64], qt, plain_f32=True)  # warm up threads / page in
+    for _ in range(max(1, warmup)):
+        O.c_matmul(x, w, qt, plain_f32=True)
+    # the timed region is `min_passes` passes; it is repeated whole until `min_seconds` have gone by
     t0 = time.perf_counter()
     passes = 0
     while True:
-        O.c_matmul(x, w, qt, plain_f32=True)
-        passes += 1
+        for _ in range(min_passes):
+            O.c_matmul(x, w, qt, plain_f32=True)
+        passes += min_passes
         dt = time.perf_counter() - t0
-        if dt >= seconds or passes >= 100000:
+        if dt >= min_seconds or dt >= 120.0:
             break
-    per_pass = algorithmic_bytes(rows, K_DIM, BATCH, 4)
-    return {"value": per_pass * passes / dt / 1e9, "unit": UNIT, "cores": O.threads(), "kind": "port",
-            "sample": f"{passes} passes over {rows} of {N_ROWS} rows of the same Q4_K weight "
-                      f"(K={K_DIM}, batch {BATCH}) in {dt:.1f} s; fused decode+dot, float32, OpenMP"}
+    per_pass = algorithmic_bytes(N_ROWS, K_DIM, BATCH, 4)
+    return {"value": per_pass * passes / dt / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+            "passes": passes, "seconds": dt,
+            "sample": f"{passes} passes over all {N_ROWS} rows of the Q4_K weight (K={K_DIM}, batch {BATCH}) in "
+                      f"{dt:.1f} s; CPU restatement of dequantize + multiply (oracle/, fused per row, float32, "
+                      f"OpenMP x{cores}) because JAX is not installed on this image"}
+
+
+def cpu_baseline() -> dict:
+    out = cpu_product(min_seconds=10.0, min_passes=3, warmup=1)
+    return {k: out[k] for k in ("value", "unit", "cores", "kind", "sample")}
 
 
 # Llama-3-70B-shaped Q4_K_M decode step: (name, qtype, rows, K) of the fused GEMVs of one layer.
@@ -189,9 +203,12 @@ def decode_leg(world: int, rank: int, dev) -> dict:
         qt = QT[qt_name]
         rows_local = rows // world
         assert rows_local * world == rows
-        # only this rank's rows are ever generated (row-sliced upload)
-        w = synth.make_weight_on_device(rows_local, k, qt, seed=seed * 64 + rank, device=dev)
-        return gj.QuantizedArray(w.data, qt, (rows_local, k))
+        # the same model at every N: a matrix is drawn whole from a seed that names only the matrix,
+        # then this rank keeps its row range (what a row-sliced upload of a model file would hold)
+        w = synth.make_weight_on_device(rows, k, qt, seed=seed, device=dev)
+        mine = w.data[rank * rows_local:(rank + 1) * rows_local].clone()
+        del w
+        return gj.QuantizedArray(mine, qt, (rows_local, k))
 
     layers = [[shard(q, n, k, 100 + 10 * li + i) for i, (_, q, n, k) in enumerate(DECODE_LAYER)]
               for li in range(DECODE_DISTINCT)]
@@ -242,10 +259,13 @@ def decode_leg(world: int, rank: int, dev) -> dict:
         h = calibrate(gu[:, :28672].contiguous(), ws[4])
     calibrate(h, head)
 
+    last_hidden = [None]
+
     def token():
         h = x0
         for li in range(DECODE_LAYERS):
             h = layer_step(h, layers[li % DECODE_DISTINCT])
+        last_hidden[0] = h
         return mm(h, head)
 
     import ctypes
@@ -299,12 +319,31 @@ def decode_leg(world: int, rank: int, dev) -> dict:
         ms = float(t.item())
     lv = value(logits).float()
     finite = bool(torch.isfinite(lv).all())
+    # parity of the last product of the chain: sampled rows of this rank's lm_head shard against the
+    # CPU checker fed with the hidden vector the chain produced; and a checksum of the logits, which
+    # must agree between runs at N = 1, 2, 4, 8 (same weights, same calibration) up to the last-place
+    # differences of a different split order
+    import numpy as np
+    from oracle import oracle as O
+    hv = value(last_hidden[0]).float().reshape(1, -1)[:, :DECODE_HEAD[3]]
+    rows_local = DECODE_HEAD[2] // world
+    pick = np.sort(np.random.default_rng(7).choice(rows_local, size=64, replace=False))
+    w_rows = head.data[torch.from_numpy(pick).to(dev)].cpu().numpy()
+    ref = O.c_matmul(O.bf16_bits(hv.cpu().numpy()), w_rows, QT[DECODE_HEAD[1]]).reshape(-1)
+    got = lv.reshape(-1)[rank * rows_local + torch.from_numpy(pick).to(dev)].cpu().numpy()
+    head_err = torch.tensor([O.rel_l2(got, ref)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(head_err, op=dist.ReduceOp.MAX)
+    checksum = {"logits_abs_mean": float(lv.abs().mean()), "logits_sum": float(lv.double().sum()),
+                "logits_first8": [float(v) for v in lv.reshape(-1)[:8]]}
     wbytes = sum(n * (k // 256) * _BLOCK_BYTES[q] for _, q, n, k in DECODE_LAYER) * DECODE_LAYERS
     wbytes += DECODE_HEAD[2] * (DECODE_HEAD[3] // 256) * _BLOCK_BYTES[DECODE_HEAD[1]]
     del graph
     return {"tok_s": 1e3 / ms, "ms_per_token": ms, "batch": 1, "launches_per_token": launches,
             "weight_gb_per_token": wbytes / 1e9, "aggregate_hbm_gbs": wbytes / (ms * 1e-3) / 1e9,
             "logits_finite": finite, "logits_rms": float(lv.pow(2).mean().sqrt()), "device_status": device_status(),
+            "parity": {"lm_head_rel_l2_vs_oracle": float(head_err.item()), "rows": 64 * world, "bar": 2e-3},
+            "checksum": checksum,
             "exchange": "tagged words stored into every rank's buffer by the kernels (ggq_gemv_sharded_tagged)" if world > 1 else "none",
             "model": "Llama-3-70B-shaped Q4_K_M (attn_v, ffn_down, lm_head in Q6_K), GEMVs only, chained",
             "note": f"{DECODE_LAYERS} layer steps cycle over {DECODE_DISTINCT} distinct synthetic layer weight sets "
@@ -312,36 +351,76 @@ def decode_leg(world: int, rank: int, dev) -> dict:
                     "magnitude; one CUDA graph per token"}
 
 
-def run_reference(args) -> None:
-    """--impl reference: the CPU route on this host's cores; rank 0 only."""
-    if int(os.environ.get("RANK", "0")) != 0:
-        return
-    import numpy as np  # noqa: F401
-    from gguf.constants import GGMLQuantizationType as QT
+def check_headline(world, rank, dev, qt, weights, x, step, y_local, use_peer, y_full) -> dict:
+    """Outside the timed region: run the timed step once more for each weight copy and compare what it
+    left behind (the whole gathered output on every rank) with the CPU checker on sampled rows of this
+    rank's shard and, on N > 1 ranks, with the one-GPU kernel on the whole weight."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
 
-    from gguf_jax_b200 import synth
+    import gguf_jax_b200 as gj
+    from gguf_jax_b200 import kernels, synth
     from oracle import oracle as O
 
-    qt = QT[QTYPE_NAME]
-    rows = 512
-    w = synth.make_weight_bytes(rows, K_DIM, qt, seed=0)
-    x = O.bf16_bits(synth.make_x(BATCH, K_DIM, seed=0))
-    for _ in range(args.warmup):
-        O.c_matmul(x, w, qt, plain_f32=True)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        O.c_matmul(x, w, qt, plain_f32=True)
-    dt = time.perf_counter() - t0
-    value = algorithmic_bytes(rows, K_DIM, BATCH, 4) * args.steps / dt / 1e9
-    sample = (f"each step = {rows} of {N_ROWS} rows of the Q4_K weight (K={K_DIM}, batch {BATCH}); "
-              "CPU restatement of dequantize + multiply (oracle/, OpenMP) because JAX is not installed")
+    rows_local = N_ROWS // world
+    worst_oracle, worst_single, exact_min, n_rows = 0.0, 0.0, 1.0, 0
+    xb = O.bf16_bits(x.float().cpu().numpy())
+    for c in range(len(weights)):
+        step(c)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        y = y_local[0]
+        if use_peer:
+            full = y.to_tensor().float().reshape(-1)
+        elif world > 1:
+            full = y_full.float().reshape(-1)
+        else:
+            full = y.float().reshape(-1)
+        pick = np.random.default_rng(100 + c).choice(rows_local, size=48, replace=False)
+        pick.sort()
+        w_rows = weights[c].data[torch.from_numpy(pick).to(dev)].cpu().numpy()
+        ref = O.c_matmul(xb, w_rows, qt).reshape(-1)
+        got = full[rank * rows_local + torch.from_numpy(pick).to(dev)].cpu().numpy()
+        worst_oracle = max(worst_oracle, O.rel_l2(got, ref))
+        n_rows += len(pick)
+        if world > 1:
+            whole = synth.make_weight_on_device(N_ROWS, K_DIM, qt, seed=c, device=dev)
+            single = kernels.fused_matmul(x, whole).float().reshape(-1)
+            del whole
+            exact_min = min(exact_min, float((single == full).float().mean()))
+            worst_single = max(worst_single, float((single - full).norm() / single.norm()))
+    if world > 1:
+        t = torch.tensor([worst_oracle, worst_single, -exact_min], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        worst_oracle, worst_single, exact_min = float(t[0]), float(t[1]), -float(t[2])
+    out = {"rows": n_rows * world, "rel_l2": worst_oracle, "bar": 2e-3,
+           "against": "oracle c_matmul (double accumulation) on 48 sampled rows per rank and weight copy"}
+    if world > 1:
+        out["vs_one_gpu_kernel"] = {"rel_l2": worst_single, "identical_fraction": exact_min,
+                                    "note": "whole gathered output of every rank against ggq_gemv on the full weight"}
+    if not worst_oracle <= 2e-3:
+        raise RuntimeError(f"headline output fails parity: {out}")
+    return out
+
+
+def run_reference(args) -> None:
+    """--impl reference: the CPU route on this host's cores; rank 0 only.  One step = one product over the
+    whole weight; at least ``--steps`` of them and at least two seconds are timed."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    out = cpu_product(min_seconds=2.0, min_passes=max(1, args.steps), warmup=max(1, min(args.warmup, 3)))
+    value = out["value"]
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "steps": max(1, args.steps), "warmup": max(1, min(args.warmup, 3)), "ms_per_step": out["seconds"] / out["passes"] * 1e3,
+        "timed_regions": out["passes"] // max(1, args.steps),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
-        "config": {"workload": f"Q4_K fused GEMV {N_ROWS}x{K_DIM} batch {BATCH}", "sample_rows": rows},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": O.threads(), "kind": "port", "sample": sample},
+        "data": "synthetic (numpy default_rng blocks, f16 super-scales |N(0,1)|*2^-7)",
+        "config": {"workload": f"Q4_K fused GEMV {N_ROWS}x{K_DIM} batch {BATCH}", "rows": N_ROWS},
+        "cpu_baseline": {k: out[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -479,7 +558,8 @@ def run_ours(args) -> None:
     # Repeat the timed region for about a second so the clock sampler sees the load.  The count
     # is decided on rank 0 and shared: every rank must replay the same number of times (the fused
     # exchange and the barriers are collective).
-    repeats = max(3, min(400, int(1200.0 / max(warm_ms, 0.01))))
+    # (~3 s: nvidia-smi needs a few hundred ms before its first sample)
+    repeats = max(3, min(3000, int(3000.0 / max(warm_ms, 0.01))))
     if world > 1:
         t = torch.tensor([repeats], device=dev)
         dist.broadcast(t, 0)
@@ -493,6 +573,8 @@ def run_ours(args) -> None:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+
+    parity = check_headline(world, rank, dev, qt, weights, x, step, y_local, use_peer[0], y_full)
 
     total_bytes = algorithmic_bytes(N_ROWS, K_DIM, BATCH) * args.steps
     value = total_bytes / (ms * 1e-3) / 1e9
@@ -553,7 +635,10 @@ def run_ours(args) -> None:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": launch_ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic (every block byte uniform random, f16 super-scales |N(0,1)|*2^-7: the seeded recipe of "
+                    "the shape's config, drawn with the device generator instead of numpy default_rng because the "
+                    "weights are generated in place on the GPU)",
             "config": {
                 "workload": f"Q4_K fused GEMV {N_ROWS}x{K_DIM} batch {BATCH} (bf16 x, bf16 y)",
                 "rows_per_gpu": rows_local, "parallelism": f"row-sharded x{world}; exchange: {exchange}" if world > 1 else "1 GPU",
@@ -575,6 +660,7 @@ def run_ours(args) -> None:
                     "ms_per_step": e2e_s / e2e_steps * 1e3,
                     "note": "weight resident on the device; activation H2D from pinned memory and result D2H every step"},
             "gpu_launches": args.steps * launches_per_step,
+            "parity": parity,
         }
         if decode is not None:
             line["decode"] = decode

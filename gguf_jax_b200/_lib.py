@@ -29,6 +29,7 @@ SIGNATURES = {
                                        ctypes.POINTER(ctypes.c_int32)]),
     "ggq_tables_bytes": (ctypes.c_size_t, []),
     "ggq_set_tables": (ctypes.c_int32, [ctypes.c_int32, ctypes.c_void_p, ctypes.c_size_t]),
+    "ggq_init": (ctypes.c_int32, [ctypes.c_int32]),
     "ggq_dequant": (ctypes.c_int32, [ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p,
                                      ctypes.c_int32, ctypes.c_void_p]),
     "ggq_has_fused": (ctypes.c_int32, [ctypes.c_int32]),

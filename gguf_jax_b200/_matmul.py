@@ -1,26 +1,25 @@
-"""``x @ w.T`` for a quantized ``w``, picking the best available route.
+"""Router for ``x @ w.T`` with a quantized ``w``.
 
-Mirror of src/gguf_jax/_matmul.py.  Three routes, chosen by :func:`matmul`:
+Public contract of the reference's router (src/gguf_jax/_matmul.py:52-260): ``matmul``,
+``dequant_matmul``, ``fused_types``, ``fused_batch_limit``; same argument meaning, same errors,
+gradient in ``x`` only.  What is behind them is this library's own:
 
-- a **fused kernel** (``ggq_gemv`` / ``ggq_gemm``), which keeps the weight quantized in
-  HBM and never materializes it;
-- **dequantize-then-matmul**, which materializes the whole weight with the decode kernel
-  and multiplies with a library GEMM;
-- the same thing **split across output rows**, when the whole weight is too large to
-  materialize at once.
+* **fused** -- one launch of the CUDA kernels over the quantized bytes.  Which kernel
+  (small-batch GEMV, or the tcgen05 GEMM above it) and up to which batch is decided by the
+  compiled library (``ggq_fused_batch_limit``), per qtype and shape; this module only asks.
+* **materialize** -- the decode kernel writes a dense bf16/f32 copy of ``w`` (all of it, or
+  ``R`` equal row slabs when the copy would exceed a byte budget) and a library GEMM multiplies.
 
-Both entry points are differentiable in ``x`` through one custom backward, whichever
-route the forward took: the backward decodes the weight again (``dx = g @ w``) in the
-same row blocks, so the only thing kept for it is the quantized payload.  No gradient
-flows to ``w``.
+The backward pass is the same for both: ``dx = g @ w`` with ``w`` decoded again slab by slab,
+so only the quantized payload is kept alive between forward and backward.
 """
 from __future__ import annotations
 
 import functools
+import math
 import os
 from typing import Callable
 
-import numpy as np
 import torch
 from gguf.constants import GGML_QUANT_SIZES
 from gguf.constants import GGMLQuantizationType as QT
@@ -30,8 +29,8 @@ from .array import QuantizedArray
 
 __all__ = ["dequant_matmul", "fused_batch_limit", "fused_types", "matmul"]
 
-# How large a temporary a single dequantize may allocate before it is split across output
-# rows, sized as 4*N*K like the reference (src/gguf_jax/_matmul.py:39-44).
+# Byte budget of one dense slab.  The reference's environment knob and default are kept
+# (src/gguf_jax/_matmul.py:39-44); like there, a slab is costed at 4 bytes per weight.
 DEQUANT_BLOCK_BYTES = int(os.environ.get("GGUF_JAX_DEQUANT_BLOCK_BYTES", 512 << 20))
 
 FusedEntry = tuple[Callable[..., torch.Tensor], Callable[[QuantizedArray], int]]
@@ -39,146 +38,143 @@ FusedEntry = tuple[Callable[..., torch.Tensor], Callable[[QuantizedArray], int]]
 
 @functools.cache
 def _fused() -> dict[QT, FusedEntry]:
-    """qtype -> (kernel, batch cap for a given weight), asked of the compiled library
-    (stands for src/gguf_jax/_matmul.py:52-75).  Raises if the library is not built."""
+    """``qtype -> (kernel, cap(w))`` for every qtype the compiled library multiplies fused.
+    Loading the library is the only way to know, so a missing build raises here."""
     L = _lib.lib()
-    table: dict[QT, FusedEntry] = {}
-    for qt in QT:
-        if qt in GGML_QUANT_SIZES and L.ggq_has_fused(int(qt)):
-            def cap(w: QuantizedArray, _qt=qt) -> int:
-                return int(L.ggq_fused_batch_limit(int(_qt), w.shape[0], w.shape[1]))
-            table[qt] = (kernels.fused_matmul, cap)
-    return table
+
+    def entry(qt: QT) -> FusedEntry:
+        code = int(qt)
+        return kernels.fused_matmul, lambda w: int(L.ggq_fused_batch_limit(code, w.shape[0], w.shape[1]))
+
+    return {qt: entry(qt) for qt in QT if qt in GGML_QUANT_SIZES and L.ggq_has_fused(int(qt))}
 
 
 def fused_types() -> list[QT]:
-    """The qtypes with a fused kernel in this installation."""
-    return sorted(_fused().keys(), key=lambda t: t.name)
+    """Qtypes that have a fused kernel, sorted by name."""
+    return sorted(_fused(), key=lambda qt: qt.name)
 
 
 def fused_batch_limit(w: QuantizedArray) -> int:
-    """Largest batch ``w`` can be multiplied at without materializing it; zero when no
-    fused kernel applies.  :func:`matmul` consults it for you."""
-    entry = _fused().get(w.qtype)
-    return entry[1](w) if entry is not None and len(w.shape) == 2 else 0
+    """Largest flattened batch at which :func:`matmul` still multiplies ``w`` without
+    materializing it (0: never)."""
+    hit = _fused().get(w.qtype)
+    return hit[1](w) if hit is not None and len(w.shape) == 2 else 0
 
 
-def matmul(x: torch.Tensor, w: QuantizedArray, *, block_bytes: int | None = None,
-           force_fused: bool = False) -> torch.Tensor:
-    """``x @ w.T`` with ``w`` quantized, by whichever route fits
-    (same contract as src/gguf_jax/_matmul.py:93-125).
-
-    ``x`` is ``(..., K)`` and the result is ``(..., N)`` for ``w`` of shape ``(N, K)``. A
-    fused kernel is used when one exists for the qtype, ``x`` is bfloat16, and the
-    flattened batch is within that kernel's range; otherwise the weight is dequantized, in
-    row blocks if it is too large to do at once.  ``force_fused`` ignores the batch cap.
-    """
+def _validate(x: torch.Tensor, w) -> None:
     if not isinstance(w, QuantizedArray):
         raise TypeError(f"expected a QuantizedArray weight, got {type(w).__name__}")
     if len(w.shape) != 2:
         raise ValueError(f"w must be 2D, got shape {w.shape}")
     if x.shape[-1] != w.shape[1]:
-        raise ValueError(
-            f"contraction mismatch: x has {x.shape[-1]}, w has {w.shape[1]}")
+        raise ValueError(f"contraction mismatch: x has {x.shape[-1]}, w has {w.shape[1]}")
 
-    kernel = None
-    entry = _fused().get(w.qtype)
-    if entry is not None and x.dtype == torch.bfloat16:
-        batch = int(np.prod(x.shape[:-1], dtype=np.int64))
-        if force_fused or batch <= entry[1](w):
-            kernel = entry[0]
-    return _frozen_matmul(x, w, kernel, _blocks(w, block_bytes))
+
+def matmul(x: torch.Tensor, w: QuantizedArray, *, block_bytes: int | None = None,
+           force_fused: bool = False) -> torch.Tensor:
+    """``x (..., K) @ w(N, K).T -> (..., N)``.
+
+    Fused when ``w.qtype`` has a kernel, ``x`` is bfloat16 and the flattened batch does not
+    exceed :func:`fused_batch_limit`; ``force_fused=True`` skips the batch test (the kernels
+    accept any batch; beyond the limit they are merely slower than materializing).  Everything
+    else is materialized under the ``block_bytes`` budget (default
+    :data:`DEQUANT_BLOCK_BYTES`).  ``TypeError`` for a weight that is not a
+    :class:`QuantizedArray`, ``ValueError`` for a weight that is not 2-D or a contraction mismatch.
+    """
+    _validate(x, w)
+    route = None
+    hit = _fused().get(w.qtype)
+    if hit is not None and x.dtype == torch.bfloat16:
+        batch = math.prod(x.shape[:-1])
+        if force_fused or batch <= hit[1](w):
+            route = hit[0]
+    return _apply(x, w, route, _slab_count(w, block_bytes))
 
 
 def dequant_matmul(x: torch.Tensor, w: QuantizedArray, *, block_bytes: int | None = None) -> torch.Tensor:
-    """``x @ w.T`` by materializing ``w`` (in row blocks when it is large), never more than
-    ``block_bytes`` of dense weight at a time (src/gguf_jax/_matmul.py:128-162)."""
+    """The materializing route on its own: decode ``w`` (in row slabs of at most ``block_bytes``
+    when it is large) and multiply with a library GEMM.  The result dtype is the promotion of
+    ``x.dtype`` and ``w.dtype``."""
     if not isinstance(w, QuantizedArray):
         raise TypeError(f"expected a QuantizedArray weight, got {type(w).__name__}")
-    return _frozen_matmul(x, w, None, _blocks(w, block_bytes))
+    return _apply(x, w, None, _slab_count(w, block_bytes))
 
 
-def _blocks(w: QuantizedArray, block_bytes: int | None) -> int:
-    return _block_count(*w.shape, DEQUANT_BLOCK_BYTES if block_bytes is None else block_bytes)
+# ---------------------------------------------------------------------------------------------
+# slabs
+
+def _block_count(out_rows: int, in_features: int, budget: int) -> int:
+    """Number of equal row slabs so that one slab, costed at 4 bytes per weight, fits ``budget``:
+    the smallest divisor of ``out_rows`` that is large enough (``out_rows`` itself if none is)."""
+    slabs_wanted = max(1, math.ceil(4 * out_rows * in_features / max(budget, 1)))
+    return next((d for d in range(slabs_wanted, out_rows) if out_rows % d == 0), out_rows) if slabs_wanted > 1 else 1
 
 
-class _FrozenMatmul(torch.autograd.Function):
-    """Forward by ``kernel`` or by dequantizing in ``blocks``; backward ``dx = g @ w`` with
-    only the quantized payload saved (src/gguf_jax/_matmul.py:170-192)."""
+def _slab_count(w: QuantizedArray, block_bytes: int | None) -> int:
+    return _block_count(w.shape[0], w.shape[1], DEQUANT_BLOCK_BYTES if block_bytes is None else block_bytes)
 
+
+def _slabs(w: QuantizedArray, count: int):
+    """``(first_row, dense slab)`` for each of ``count`` equal row slabs, decoded one at a time."""
+    rows = w.shape[0] // count
+    for i in range(count):
+        part = QuantizedArray(w.data[i * rows:(i + 1) * rows], w.qtype, (rows, w.shape[1]), w.dtype)
+        yield i * rows, part.dequantize()
+
+
+def _promoted_mm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    common = torch.promote_types(a.dtype, b.dtype)
+    return torch.matmul(a.to(common), b.to(common))
+
+
+def _materialized_forward(x: torch.Tensor, w: QuantizedArray, count: int) -> torch.Tensor:
+    n_out = w.shape[0]
+    x2 = x.reshape(-1, w.shape[1])
+    y = None
+    for row0, dense in _slabs(w, count):
+        part = _promoted_mm(x2, dense.T)
+        if count == 1:
+            y = part
+            break
+        if y is None:
+            y = part.new_empty((x2.shape[0], n_out))
+        y[:, row0:row0 + dense.shape[0]] = part
+    return y.reshape(*x.shape[:-1], n_out)
+
+
+def _input_cotangent(g: torch.Tensor, w: QuantizedArray, count: int) -> torch.Tensor:
+    """``g (..., N) @ w (N, K)``: the slabs cut the contraction, so their products add up (in
+    float32 when there is more than one)."""
+    g2 = g.reshape(-1, w.shape[0])
+    if count == 1:
+        (_, dense), = _slabs(w, 1)
+        return _promoted_mm(g2, dense).reshape(*g.shape[:-1], w.shape[1])
+    total = torch.zeros((g2.shape[0], w.shape[1]), dtype=torch.float32, device=g.device)
+    for row0, dense in _slabs(w, count):
+        total += _promoted_mm(g2[:, row0:row0 + dense.shape[0]], dense).float()
+    return total.reshape(*g.shape[:-1], w.shape[1])
+
+
+# ---------------------------------------------------------------------------------------------
+# one differentiable wrapper around whichever forward was chosen
+
+class _QuantizedLinear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, data, qtype, shape, dtype, kernel, blocks):
-        w = QuantizedArray(data=data, qtype=qtype, shape=shape, dtype=dtype)
-        ctx.save_for_backward(data)
-        ctx.meta = (qtype, shape, dtype, blocks, x.dtype)
-        if kernel is not None:
-            return kernel(x, w)
-        return _dequant_forward(x, w, blocks)
+    def forward(ctx, x, payload, meta, route, count):
+        ctx.save_for_backward(payload)
+        ctx.extra = (meta, count, x.dtype)
+        w = QuantizedArray(payload, *meta)
+        return route(x, w) if route is not None else _materialized_forward(x, w, count)
 
     @staticmethod
     def backward(ctx, g):
-        (data,) = ctx.saved_tensors
-        qtype, shape, dtype, blocks, x_dtype = ctx.meta
-        w = QuantizedArray(data=data, qtype=qtype, shape=shape, dtype=dtype)
-        return _dequant_backward(g, w, blocks).to(x_dtype), None, None, None, None, None, None
+        (payload,) = ctx.saved_tensors
+        meta, count, x_dtype = ctx.extra
+        dx = _input_cotangent(g, QuantizedArray(payload, *meta), count).to(x_dtype)
+        return dx, None, None, None, None
 
 
-def _frozen_matmul(x, w: QuantizedArray, kernel, blocks: int) -> torch.Tensor:
-    if torch.is_grad_enabled() and x.requires_grad:
-        return _FrozenMatmul.apply(x, w.data, w.qtype, w.shape, w.dtype, kernel, blocks)
-    if kernel is not None:
-        return kernel(x, w)
-    return _dequant_forward(x, w, blocks)
-
-
-def _mm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """``a @ b`` with numpy-style dtype promotion (an f16 ``x`` against a bf16 weight
-    promotes to f32, as in the reference)."""
-    dt = torch.promote_types(a.dtype, b.dtype)
-    return torch.matmul(a.to(dt), b.to(dt))
-
-
-def _dequant_forward(x: torch.Tensor, w: QuantizedArray, blocks: int) -> torch.Tensor:
-    out_rows, in_features = w.shape
-    if blocks == 1:
-        return _mm(x, w.dequantize().T)
-    rows = out_rows // blocks
-    flat = x.reshape(-1, in_features)
-    data = w.data.reshape(blocks, rows, -1)
-    out = None
-    for i in range(blocks):
-        sub = QuantizedArray(data=data[i], qtype=w.qtype, shape=(rows, in_features), dtype=w.dtype)
-        part = _mm(flat, sub.dequantize().T)
-        if out is None:
-            out = torch.empty((flat.shape[0], out_rows), dtype=part.dtype, device=part.device)
-        out[:, i * rows:(i + 1) * rows] = part
-    return out.reshape(*x.shape[:-1], out_rows)
-
-
-def _dequant_backward(g: torch.Tensor, w: QuantizedArray, blocks: int) -> torch.Tensor:
-    """``g @ w``, the cotangent of ``x``, decoding ``w`` as the forward did; row blocks
-    partition the contraction, so their products are summed in float32."""
-    out_rows, in_features = w.shape
-    if blocks == 1:
-        return _mm(g, w.dequantize())
-    rows = out_rows // blocks
-    flat = g.reshape(-1, out_rows)
-    data = w.data.reshape(blocks, rows, -1)
-    acc = torch.zeros((flat.shape[0], in_features), dtype=torch.float32, device=g.device)
-    for i in range(blocks):
-        sub = QuantizedArray(data=data[i], qtype=w.qtype, shape=(rows, in_features), dtype=w.dtype)
-        acc += _mm(flat[:, i * rows:(i + 1) * rows], sub.dequantize()).float()
-    return acc.reshape(*g.shape[:-1], in_features)
-
-
-def _block_count(out_rows: int, in_features: int, budget: int) -> int:
-    """How many row blocks keep one dequantize under ``budget``; constrained to divisors
-    of ``out_rows`` so the blocks are uniform (src/gguf_jax/_matmul.py:247-260)."""
-    needed = 4 * out_rows * in_features
-    if needed <= budget:
-        return 1
-    target = -(-needed // budget)
-    for n in range(target, out_rows + 1):
-        if out_rows % n == 0:
-            return n
-    return out_rows
+def _apply(x: torch.Tensor, w: QuantizedArray, route, count: int) -> torch.Tensor:
+    if x.requires_grad and torch.is_grad_enabled():
+        return _QuantizedLinear.apply(x, w.data, (w.qtype, w.shape, w.dtype), route, count)
+    return route(x, w) if route is not None else _materialized_forward(x, w, count)

@@ -1,12 +1,15 @@
-"""QuantizedArray: a pytree holding a GGUF-quantized tensor on the device.
+"""QuantizedArray: GGUF block bytes on the device plus what is needed to decode them.
 
-Mirror of src/gguf_jax/array.py with torch tensors as the array type: same fields, same
-methods, same errors.  The uint8 payload layout ``(*shape[:-1], row_bytes)`` is the ABI
-the CUDA kernels read directly.
+Public contract of the reference's container (src/gguf_jax/array.py:33-119): the fields
+``data / qtype / shape / dtype``, the properties ``ndim / size / nbytes``, ``astype``,
+``dequantize``, ``from_bytes`` and the module-level ``quantize``, with the same errors.
+Here the array type is a torch tensor and the payload layout ``uint8[*shape[:-1], row_bytes]``
+is exactly what the CUDA kernels index, so a row range of a 2-D weight is a byte slice.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field, replace
+import dataclasses
+import math
 from typing import Any
 
 import numpy as np
@@ -18,127 +21,124 @@ from . import _backend, quants
 
 __all__ = ["QuantizedArray", "quantize"]
 
-# Types kept as native (non-uint8) arrays: dequantize is a cast (or identity).
-_NATIVE_TYPES = {
-    GGMLQuantizationType.I8: torch.int8,
-    GGMLQuantizationType.I16: torch.int16,
-    GGMLQuantizationType.I32: torch.int32,
-    GGMLQuantizationType.I64: torch.int64,
-    GGMLQuantizationType.F64: torch.float64,
+_QT = GGMLQuantizationType
+# GGUF also stores plain integer / float64 tensors.  They are held in their own element type
+# instead of as bytes; the flag says whether "dequantize" leaves them alone (integers) or casts.
+_PLAIN: dict[GGMLQuantizationType, tuple[torch.dtype, bool]] = {
+    _QT.I8: (torch.int8, True), _QT.I16: (torch.int16, True), _QT.I32: (torch.int32, True),
+    _QT.I64: (torch.int64, True), _QT.F64: (torch.float64, False),
 }
-
-_INTEGER_TYPES = {
-    GGMLQuantizationType.I8,
-    GGMLQuantizationType.I16,
-    GGMLQuantizationType.I32,
-    GGMLQuantizationType.I64,
-}
+# Used by the loader to decide whether a tensor's bytes need a uint8 view.
+_NATIVE_TYPES = {qt: spec[0] for qt, spec in _PLAIN.items()}
 
 
-@dataclass
+def _row_bytes(qtype: GGMLQuantizationType, n_cols: int) -> int:
+    per_block, block_bytes = GGML_QUANT_SIZES[qtype]
+    return n_cols // per_block * block_bytes
+
+
+@dataclasses.dataclass
 class QuantizedArray:
-    """A quantized tensor: raw GGUF block data plus the metadata to decode it.
+    """One tensor of a GGUF file, still in its storage format.
 
-    ``data`` is the payload as stored in the GGUF file: a uint8 tensor of shape
-    ``(*shape[:-1], row_bytes)`` for quantized/float qtypes (F16/F32/BF16 included), or a
-    native integer/float tensor for the plain I8/I16/I32/I64/F64 types.
-
-    It is a pytree with exactly one leaf (``data``); ``qtype``, ``shape`` and ``dtype`` are
-    static metadata (src/gguf_jax/array.py:33-50).
+    ``data``   the only tensor inside (and the only pytree leaf): ``uint8[*shape[:-1], row_bytes]``
+               for every block format and for F16/F32/BF16, or an int8/16/32/64 / float64 tensor
+               of ``shape`` for the plain GGUF element types;
+    ``qtype``  the GGML storage format;
+    ``shape``  logical shape after decoding;
+    ``dtype``  what :meth:`dequantize` returns when not told otherwise.
+    The last three are static metadata: tree maps see one leaf and carry them along.
     """
 
     data: torch.Tensor
-    qtype: GGMLQuantizationType = field(metadata={"static": True})
-    shape: tuple[int, ...] = field(metadata={"static": True})
-    dtype: Any = field(default=torch.bfloat16, metadata={"static": True})
+    qtype: GGMLQuantizationType = dataclasses.field(metadata={"static": True})
+    shape: tuple[int, ...] = dataclasses.field(metadata={"static": True})
+    dtype: Any = dataclasses.field(default=torch.bfloat16, metadata={"static": True})
 
+    # ---- shape-like properties of the logical tensor
     @property
     def ndim(self) -> int:
         return len(self.shape)
 
     @property
     def size(self) -> int:
-        return int(np.prod(self.shape)) if self.shape else 1
+        return math.prod(self.shape)
 
     @property
     def nbytes(self) -> int:
-        return self.data.numel() * self.data.element_size()
+        """Bytes held in device memory (the quantized payload, not the decoded size)."""
+        return self.data.element_size() * self.data.numel()
 
     @property
     def device(self) -> torch.device:
         return self.data.device
 
+    def __repr__(self) -> str:
+        return f"QuantizedArray({self.qtype.name}, shape={self.shape}, dtype={str(self.dtype).removeprefix('torch.')})"
+
+    # ---- cheap views
     def to(self, device) -> "QuantizedArray":
-        """Same array with the payload moved to ``device``."""
-        return replace(self, data=self.data.to(device))
+        """The same tensor with its payload on ``device``."""
+        return dataclasses.replace(self, data=self.data.to(device))
 
     def astype(self, dtype) -> "QuantizedArray":
-        """Return a copy whose default dequantization dtype is ``dtype``."""
-        return replace(self, dtype=_backend.canon_dtype(dtype))
+        """Same payload, different default output dtype for :meth:`dequantize`."""
+        return dataclasses.replace(self, dtype=_backend.canon_dtype(dtype))
 
+    # ---- decoding
     def dequantize(self, dtype=None) -> torch.Tensor:
-        """Decode to a dense tensor of ``dtype`` (default: ``self.dtype``).
+        """Dense tensor of ``shape``.  Block formats go through the CUDA decode kernel: float32
+        arithmetic bit-identical to ``gguf.quants.dequantize``, rounded once to the requested
+        dtype inside the kernel.  Plain integer tensors come back unchanged, float64 is cast."""
+        want = self.dtype if dtype is None else _backend.canon_dtype(dtype)
+        plain = _PLAIN.get(self.qtype)
+        if plain is None:
+            return quants.dequantize(self.data, self.qtype, want).reshape(self.shape)
+        dense = self.data.reshape(self.shape)
+        return dense if plain[1] else dense.to(want)
 
-        Decoding computes in float32, bitwise identical to ``gguf.quants.dequantize``, and
-        rounds once to ``dtype`` inside the kernel. Integer qtypes are returned as-is.
-        """
-        dtype = self.dtype if dtype is None else _backend.canon_dtype(dtype)
-        if self.qtype in _NATIVE_TYPES:
-            out = self.data.reshape(self.shape)
-            if self.qtype in _INTEGER_TYPES:
-                return out
-            return out.to(dtype)
-        return quants.dequantize(self.data, self.qtype, dtype).reshape(self.shape)
-
-    def __repr__(self) -> str:
-        name = str(self.dtype).replace("torch.", "")
-        return f"QuantizedArray({self.qtype.name}, shape={self.shape}, dtype={name})"
-
+    # ---- construction
     @classmethod
     def from_bytes(cls, data, qtype: GGMLQuantizationType, shape: tuple[int, ...] | None = None,
                    dtype=torch.bfloat16, device=None) -> "QuantizedArray":
-        """Wrap raw quantized bytes (numpy or torch uint8, byte-shaped) as a QuantizedArray
-        (src/gguf_jax/array.py:87-104)."""
-        data = _backend.as_tensor(data, device)
-        dtype = _backend.canon_dtype(dtype)
-        if qtype in _NATIVE_TYPES:
-            shape = tuple(data.shape) if shape is None else tuple(shape)
-            return cls(data=data.reshape(shape), qtype=qtype, shape=shape, dtype=dtype)
-        if data.dtype != torch.uint8:
-            raise ValueError(f"expected uint8 data for {qtype.name}, got {data.dtype}")
+        """Wrap a payload (numpy array, torch tensor or buffer) without touching its bytes.
+
+        For block formats ``data`` must be uint8 (``ValueError`` otherwise) shaped
+        ``(..., row_bytes)``; ``shape`` defaults to what that byte shape implies
+        (``row_bytes / block_bytes * block_elems`` columns) and, when given, the payload is
+        reshaped to match it.  Plain integer / float64 tensors keep their element type.
+        """
+        payload = _backend.as_tensor(data, device)
+        out_dtype = _backend.canon_dtype(dtype)
+        if qtype in _PLAIN:
+            logical = tuple(payload.shape) if shape is None else tuple(int(s) for s in shape)
+            return cls(payload.reshape(logical), qtype, logical, out_dtype)
+        if payload.dtype != torch.uint8:
+            raise ValueError(f"expected uint8 data for {qtype.name}, got {payload.dtype}")
         if shape is None:
-            shape = quants._ref.quant_shape_from_byte_shape(tuple(data.shape), qtype)
-        shape = tuple(int(s) for s in shape)
-        block_size, type_size = GGML_QUANT_SIZES[qtype]
-        expected = shape[-1] // block_size * type_size
-        data = data.reshape(*shape[:-1], expected)
-        return cls(data=data, qtype=qtype, shape=shape, dtype=dtype)
-
-
-def _flatten(a: QuantizedArray):
-    return [a.data], (a.qtype, a.shape, a.dtype)
-
-
-def _unflatten(leaves, ctx):
-    return QuantizedArray(leaves[0], *ctx)
+            logical = tuple(quants._ref.quant_shape_from_byte_shape(tuple(payload.shape), qtype))
+        else:
+            logical = tuple(int(s) for s in shape)
+        payload = payload.reshape(*logical[:-1], _row_bytes(qtype, logical[-1]))
+        return cls(payload, qtype, logical, out_dtype)
 
 
 _pytree.register_pytree_node(
-    QuantizedArray, _flatten, _unflatten,
+    QuantizedArray,
+    lambda qa: ([qa.data], (qa.qtype, qa.shape, qa.dtype)),
+    lambda leaves, meta: QuantizedArray(leaves[0], *meta),
     serialized_type_name="gguf_jax_b200.QuantizedArray")
 
 
 def quantize(array, qtype: GGMLQuantizationType, dtype=torch.bfloat16, device=None) -> QuantizedArray:
-    """Quantize an array on the host through gguf-py (src/gguf_jax/array.py:107-119).
-
-    Only the qtypes gguf-py can quantize are supported; a convenience for tests and tools.
-    """
+    """Host-side quantization through gguf-py, for the formats gguf-py can encode
+    (src/gguf_jax/array.py:107-119); meant for tests and small tools, not for a hot path."""
     import gguf
 
     if isinstance(array, torch.Tensor):
-        array = array.detach().to("cpu", torch.float32).numpy()
-    np_arr = np.asarray(array, dtype=np.float32)
-    qdata = gguf.quants.quantize(np_arr, qtype)
-    if qdata.dtype != np.uint8:
-        qdata = np.ascontiguousarray(qdata).view(np.uint8)
-    return QuantizedArray.from_bytes(qdata, qtype, shape=np_arr.shape, dtype=dtype, device=device)
+        array = array.detach().cpu().float().numpy()
+    dense = np.asarray(array, dtype=np.float32)
+    packed = np.ascontiguousarray(gguf.quants.quantize(dense, qtype))
+    if packed.dtype != np.uint8:
+        packed = packed.view(np.uint8)
+    return QuantizedArray.from_bytes(packed, qtype, shape=dense.shape, dtype=dtype, device=device)

@@ -44,7 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(HERE, "..", "include", "ggq.h"))
     env = dict(os.environ)
-    # nvcc's host compiler: the image exports CC/CXX to a wrapper; use the system g++.
+    # nvcc's host compiler: prefer the system g++ over whatever CC/CXX point to.
     ccbin = ["-ccbin", "/usr/bin/g++"] if os.path.exists("/usr/bin/g++") else []
 
     def compile_one(src: str) -> str:

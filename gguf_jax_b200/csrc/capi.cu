@@ -1,4 +1,5 @@
 // Library-level pieces of the C ABI: type table, error text, per-device codebook tables.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
@@ -37,20 +38,55 @@ int32_t fail(int32_t status, const char* fmt, ...) {
 }
 
 constexpr int kMaxDevices = 64;
+// Everything the library keeps per device.  Each member is created at most once (std::call_once)
+// and never freed or moved afterwards, so readers need no lock.
 struct DeviceState {
-  uint8_t* tables = nullptr;
-  int* status = nullptr;
+  std::once_flag status_once, sm_once;
+  std::mutex tables_mu;
+  std::atomic<uint8_t*> tables{nullptr};
+  std::atomic<int*> status{nullptr};
+  std::atomic<int> sm_count{0};
 };
 static DeviceState g_dev[kMaxDevices];
-static std::mutex g_mu;
 
 const uint8_t* device_tables(int device) {
   if (device < 0 || device >= kMaxDevices) return nullptr;
-  return g_dev[device].tables;
+  return g_dev[device].tables.load(std::memory_order_acquire);
 }
+
+// The status word is allocated the first time a launcher that can raise it runs on the device
+// (or by ggq_init), independently of the codebook tables.  That first call allocates device
+// memory and must therefore be made outside stream capture.
 int* device_status_word(int device) {
   if (device < 0 || device >= kMaxDevices) return nullptr;
-  return g_dev[device].status;
+  DeviceState& d = g_dev[device];
+  std::call_once(d.status_once, [&] {
+    int prev = 0;
+    cudaGetDevice(&prev);
+    int* s = nullptr;
+    cudaError_t err = cudaSetDevice(device);
+    if (err == cudaSuccess) err = cudaMalloc(&s, 256);
+    if (err == cudaSuccess) err = cudaMemset(s, 0, 256);
+    cudaSetDevice(prev);
+    if (err != cudaSuccess) {
+      if (s) cudaFree(s);
+      (void)cudaGetLastError();
+      s = nullptr;
+    }
+    d.status.store(s, std::memory_order_release);
+  });
+  return d.status.load(std::memory_order_acquire);
+}
+
+int device_sm_count(int device) {
+  if (device < 0 || device >= kMaxDevices) return 0;
+  DeviceState& d = g_dev[device];
+  std::call_once(d.sm_once, [&] {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
+    d.sm_count.store(n, std::memory_order_release);
+  });
+  return d.sm_count.load(std::memory_order_acquire);
 }
 
 }  // namespace ggq
@@ -75,25 +111,28 @@ extern "C" int32_t ggq_set_tables(int32_t device, const void* host_blob, size_t 
   if (device < 0 || device >= kMaxDevices) return fail(GGQ_BAD_SHAPE, "ggq_set_tables: device %d", device);
   if (bytes != TAB_BYTES || !host_blob)
     return fail(GGQ_BAD_SHAPE, "ggq_set_tables: blob must be %d bytes, got %zu", (int)TAB_BYTES, bytes);
-  std::lock_guard<std::mutex> lock(g_mu);
-  if (g_dev[device].tables) return GGQ_OK;
+  DeviceState& d = g_dev[device];
+  std::lock_guard<std::mutex> lock(d.tables_mu);
+  if (d.tables.load(std::memory_order_acquire)) return GGQ_OK;
   int prev = 0;
   cudaGetDevice(&prev);
   cudaError_t err = cudaSetDevice(device);
   uint8_t* t = nullptr;
-  int* s = nullptr;
   if (err == cudaSuccess) err = cudaMalloc(&t, TAB_BYTES);
-  if (err == cudaSuccess) err = cudaMalloc(&s, 256);
   if (err == cudaSuccess) err = cudaMemcpy(t, host_blob, TAB_BYTES, cudaMemcpyHostToDevice);
-  if (err == cudaSuccess) err = cudaMemset(s, 0, 256);
   cudaSetDevice(prev);
   if (err != cudaSuccess) {
     if (t) cudaFree(t);
-    if (s) cudaFree(s);
     return fail(GGQ_LAUNCH_FAILED, "ggq_set_tables: %s", cudaGetErrorString(err));
   }
-  g_dev[device].status = s;
-  g_dev[device].tables = t;
+  d.tables.store(t, std::memory_order_release);
+  return GGQ_OK;
+}
+
+extern "C" int32_t ggq_init(int32_t device) {
+  if (device < 0 || device >= kMaxDevices) return fail(GGQ_BAD_SHAPE, "ggq_init: device %d", device);
+  if (!device_status_word(device)) return fail(GGQ_LAUNCH_FAILED, "ggq_init: could not allocate the status word on device %d", device);
+  if (device_sm_count(device) <= 0) return fail(GGQ_LAUNCH_FAILED, "ggq_init: device %d reports no multiprocessors", device);
   return GGQ_OK;
 }
 
@@ -105,8 +144,9 @@ extern "C" int32_t ggq_has_fused(int32_t qtype) {
 extern "C" int32_t ggq_read_status(int32_t device, int32_t* status_word) {
   if (!status_word) return fail(GGQ_BAD_SHAPE, "ggq_read_status: null out pointer");
   *status_word = 0;
-  int* s = device_status_word(device);
-  if (!s) return GGQ_OK;  // nothing ever ran on this device
+  if (device < 0 || device >= kMaxDevices) return fail(GGQ_BAD_SHAPE, "ggq_read_status: device %d", device);
+  int* s = g_dev[device].status.load(std::memory_order_acquire);
+  if (!s) return GGQ_OK;  // no launcher that can raise it has run on this device
   int prev = 0;
   cudaGetDevice(&prev);
   cudaSetDevice(device);

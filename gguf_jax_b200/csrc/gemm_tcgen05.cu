@@ -375,15 +375,15 @@ static cudaError_t launch(const uint8_t* w, int64_t N, int64_t K, const void* x,
   const Layout lay(tile_m_max, raw_pitch<QT>());
   if (lay.stages < 2) return cudaErrorInvalidValue;
   const int smem = lay.total();
-  static bool attr_done[64] = {};
+  static std::atomic<bool> attr_done[64];   // setting the attribute twice is harmless, so a flag per device suffices
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+  if (dev >= 0 && dev < 64 && !attr_done[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<QT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(gemm_tf32_kernel<QT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return e;
-    attr_done[dev] = true;
+    attr_done[dev].store(true, std::memory_order_release);
   }
   dim3 grid((unsigned)((N + kTileN - 1) / kTileN), (unsigned)((M + kMaxTileM - 1) / kMaxTileM), (unsigned)splits);
   if (tile_m_max > 128)

@@ -28,12 +28,7 @@ extern "C" int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K) {
   return kGemvMaxBatch;
 }
 
-static int sm_count_of(int dev) {
-  static int cached[64] = {};
-  if (dev < 0 || dev >= 64) return 0;
-  if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
-  return cached[dev];
-}
+static int sm_count_of(int dev) { return device_sm_count(dev); }
 
 extern "C" size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32_t M) {
   const TypeInfo* ti = type_info(qtype);
@@ -92,7 +87,7 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
     for (int m = 0; m < M && err == cudaSuccess; m++)
       err = tuned((const uint8_t*)w, N, K, (const uint8_t*)x_bf16 + (size_t)m * K * 2,
                   (uint8_t*)y + (size_t)m * N * y_item, y_dtype, workspace, workspace_bytes, sm_count_of(dev),
-                  device_status_word(dev), st, nullptr);
+                  nullptr, st, nullptr);   // no bounded wait on this path: no status word needed
   } else if (gemv_mma_applicable(ti, N, K, M) && M >= kMmaMinBatch) {
     err = gemv_mma(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, st);
   } else if (gemv_stream_applicable(ti, N, K, M, w, x_bf16)) {

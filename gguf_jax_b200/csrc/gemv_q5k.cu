@@ -246,7 +246,7 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
       auto fetch = [&](int sblk, uint4 (&v)[4]) {
 #pragma unroll
         for (int q = 0; q < 4; q++)
-          v[q] = pp.x_tagged ? peer_load8_tagged(pp.x_tagged, sblk * 4 + q, x_tag, status) : __ldg(xg + sblk * 4 + q);
+          v[q] = pp.x_tagged ? peer_load8_tagged(pp.x_tagged, sblk * 4 + q, x_tag, status) : __ldcg(xg + sblk * 4 + q);   // L2-coherent: x may have been stored by peers or by the previous launch while this kernel was already resident
       };
       auto convert = [&](int sblk, const uint4 (&v)[4]) {
         const float up = (sblk & 1) ? up_odd : up_even;
@@ -415,15 +415,15 @@ cudaError_t gemv_q5k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
   while (depth > 2 && Smem(depth).total((int)K) > kSmemLimit) depth--;
   const int smem = Smem(depth).total((int)K);
   if (smem > kSmemLimit) return cudaErrorInvalidValue;
-  static bool attr_done[64] = {};
+  static std::atomic<bool> attr_done[64];   // setting the attribute twice is harmless, so a flag per device suffices
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+  if (dev >= 0 && dev < 64 && !attr_done[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return e;
-    attr_done[dev] = true;
+    attr_done[dev].store(true, std::memory_order_release);
   }
   float* partials = reinterpret_cast<float*>(ws);
   int* counters = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ws) + kWsCounterOffset);

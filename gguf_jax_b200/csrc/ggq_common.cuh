@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/ggq.h"
 
 namespace ggq {
@@ -47,7 +49,8 @@ inline int block_alignment(const TypeInfo* ti) {
 
 // Per-device immutable state owned by the library (capi.cu).
 const uint8_t* device_tables(int device);    // nullptr until ggq_set_tables(device, ...)
-int* device_status_word(int device);         // allocated lazily with the tables
+int* device_status_word(int device);         // allocated on first use (or by ggq_init), nullptr if that failed
+int device_sm_count(int device);             // multiprocessor count, cached per device; 0 if unknown
 
 // Thread-local error text (capi.cu).
 int32_t fail(int32_t status, const char* fmt, ...);

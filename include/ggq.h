@@ -11,6 +11,8 @@
  *
  * Every function that returns int32_t returns a ggq_status; 0 is success.  On failure a
  * thread-local message is available from ggq_last_error().  Nothing throws or exits.
+ * All entry points may be called from several host threads at once; the library's own state
+ * is per device and created once under std::call_once.
  *
  * Each declaration names the interface of the reference project (nshepperd/gguf-jax) it
  * stands in for, as path:line inside that project.
@@ -62,6 +64,13 @@ size_t ggq_tables_bytes(void);
 /* Upload the codebook blob (host memory) to `device` once.  The library keeps this one
  * immutable allocation per device until the process exits.  Idempotent. */
 int32_t ggq_set_tables(int32_t device, const void* host_blob, size_t bytes);
+
+/* Optional per-device set-up: allocates the 4-byte device status word that bounded device-side
+ * waits raise (see ggq_read_status) and caches the multiprocessor count.  The launchers that can
+ * wait (ggq_gemv_sharded, ggq_gemv_sharded_tagged, ggq_gemm) do the same on their first call on
+ * a device; that first call allocates device memory, so make it -- or this call -- outside any
+ * stream capture.  Thread-safe, idempotent.  No reference counterpart. */
+int32_t ggq_init(int32_t device);
 
 /* Decode n_blocks blocks of `qtype` (device bytes, n_blocks * block_bytes) into
  * n_blocks * block_elems values of out_dtype on `stream`.  The float32 result is
@@ -172,8 +181,10 @@ int32_t ggq_gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x_b
                             int32_t y_dtype, void* stream);
 
 /* Reads and clears the device-side status word of `device` (0 = no bounded wait ran
- * out since the last read).  Synchronises the device.  No reference counterpart: the
- * reference has no device-side waits. */
+ * out since the last read; otherwise the call returns GGQ_TIMEOUT).  Synchronises the device.
+ * The word exists from the first ggq_init / sharded / ggq_gemm call on the device, whether or
+ * not ggq_set_tables was ever called; before that the function reports 0.  No reference
+ * counterpart: the reference has no device-side waits. */
 int32_t ggq_read_status(int32_t device, int32_t* status_word);
 
 #ifdef __cplusplus

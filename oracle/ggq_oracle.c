@@ -528,3 +528,15 @@ int ggq_oracle_threads(void) {
   return 1;
 #endif
 }
+
+/* Number of OpenMP threads later calls use (n < 1: leave as is).  Launchers such as torchrun
+ * export OMP_NUM_THREADS=1 to their children; a timed CPU baseline sets the count explicitly. */
+int ggq_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}

@@ -83,6 +83,12 @@ def threads() -> int:
     return int(lib().ggq_oracle_threads())
 
 
+def set_threads(n: int) -> int:
+    """Use ``n`` OpenMP threads from now on (launchers like torchrun export OMP_NUM_THREADS=1);
+    returns the count in effect."""
+    return int(lib().ggq_oracle_set_threads(int(n)))
+
+
 # ---------------------------------------------------------------------------------------
 # decode
 

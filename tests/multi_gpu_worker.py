@@ -21,9 +21,11 @@ from oracle import oracle as O  # noqa: E402
 
 
 def same(a, b, what):
-    """Equal up to float32 summation order: where a row group is cut between CTAs depends on the
-    number of rows, so a sharded and an unsharded launch may add partial sums in a different
-    order; after the bf16 rounding that shows as a last-place difference in a few outputs."""
+    """Sharded against unsharded result of the same kernel.  Not bitwise in general: where the K
+    range of a row is cut between CTAs depends on how many rows the launch has, so the float32
+    partial sums of a row may be added in a different order in a launch over N/P rows than in a
+    launch over N rows.  The pinned bound: float32 sums differ by a few ulps, so after the single
+    bf16 rounding at most 2 % of the outputs may differ, each by one place (2^-7 relative)."""
     a, b = a.float(), b.float()
     exact = (a == b).float().mean().item()
     assert exact >= 0.98, f"{what}: only {exact:.3f} of the outputs identical"
@@ -61,9 +63,47 @@ def main():
         dist.barrier()
         torch.cuda.synchronize()
         same(y, single, f"rank {rank}: fused exchange, step {step}")
+    # flag exchange, chained: the output of exchange i (written by every rank into every rank's
+    # buffer while the consumer kernel may already be resident) is the activation of launch i + 1
+    nk = 2048
+    fchain = [QT.Q4_K, QT.Q6_K, QT.Q5_K, QT.Q4_K, QT.Q6_K, QT.Q4_K]
+    f_full = [gj.QuantizedArray.from_bytes(synth.make_weight_bytes(nk, nk, qt, seed=60 + i), qt, shape=(nk, nk), device=dev)
+              for i, qt in enumerate(fchain)]
+    f_shards = [sharded.shard_rows(w, rank, world) for w in f_full]
+    fout = sharded.PeerOutput(None, max_batch=1, n_total=nk, device=dev, n_buffers=len(fchain))
+    fx0 = torch.from_numpy(synth.make_x(1, nk, seed=61)).to(dev).to(torch.bfloat16)
+
+    def run_flag_chain():
+        ys, cur = [], fx0
+        for i, sh in enumerate(f_shards):
+            cur = fout.matmul(cur, sh, wait_previous=i > 0)
+            ys.append(cur)
+        return ys
+
+    def check_flag_chain(ys, what):
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        vals = [y.clone() for y in ys]
+        for i, w in enumerate(f_full):
+            single = kernels.fused_matmul(fx0 if i == 0 else vals[i - 1], w)
+            same(vals[i], single, f"rank {rank}: flag chain {what}, launch {i}")
+        dist.barrier()
+
+    check_flag_chain(run_flag_chain(), "eager")
+    fst = torch.cuda.Stream(dev)
+    with torch.cuda.stream(fst):
+        fg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(fg, stream=fst):
+            f_outs = run_flag_chain()
+    for rep in range(2):
+        with torch.cuda.stream(fst):
+            fg.replay()
+        fst.synchronize()
+        check_flag_chain(f_outs, f"graph replay {rep}")
+
     # tagged exchange: a chain whose products feed each other (n = k), including a result consumed
     # two launches later, then the same chain captured in a CUDA graph and replayed
-    nk = 2048
     chain = [QT.Q4_K, QT.Q6_K, QT.Q5_K, QT.Q6_K, QT.Q4_K]
     ws_full = [gj.QuantizedArray.from_bytes(synth.make_weight_bytes(nk, nk, qt, seed=40 + i), qt, shape=(nk, nk), device=dev)
                for i, qt in enumerate(chain)]
@@ -109,7 +149,7 @@ def main():
     assert _lib.lib().ggq_read_status(dev.index, ctypes.byref(word)) == 0 and word.value == 0
     dist.barrier()
     if rank == 0:
-        print("MULTI_GPU_OK", flush=True)
+        print(f"MULTI_GPU_OK world={world}", flush=True)
     sys.stdout.flush()
     os._exit(0)
 
