@@ -72,5 +72,27 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_xla_ffi(verbose: bool = False) -> str | None:
+    """Compile csrc/xla_ffi.cc (the jax.ffi handlers over the C ABI) into libggq_xla_ffi.so when the
+    XLA FFI headers are available, i.e. when ``import jax.ffi`` works; returns None otherwise."""
+    try:
+        import jax.ffi as jffi
+    except Exception:  # noqa: BLE001 -- no jaxlib on this machine: nothing to build against
+        return None
+    build()
+    out = os.path.join(HERE, "libggq_xla_ffi.so")
+    src = os.path.join(CSRC, "xla_ffi.cc")
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+    cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", f"-I{jffi.include_dir()}", f"-I{os.path.join(HERE, '..', 'include')}",
+           "-I/usr/local/cuda/include", src, f"-L{HERE}", "-lggq_b200", f"-Wl,-rpath,{HERE}", "-o", out]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"xla_ffi.cc failed to compile:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print("XLA FFI adapter:", build_xla_ffi(verbose="--verbose" in sys.argv) or "skipped (jax.ffi is not importable here)")

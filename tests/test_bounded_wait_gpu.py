@@ -94,5 +94,5 @@ def test_flag_wait_runs_out_and_reports_timeout():
     assert _status(L) == (0, 0)
     # rows 0..n-1 of both outputs were still written by the launch that gave up
     ref = O.c_matmul(O.bf16_bits(x.float().cpu().numpy()), w.cpu().numpy(), QT.Q4_K)
-    assert O.rel_l2(y1[:n].float().cpu().numpy().reshape(1, n), ref) <= 2e-3
+    np.testing.assert_allclose(y1[:n].float().cpu().numpy().reshape(1, n), ref, rtol=1e-2, atol=1e-2 * np.abs(ref).max())
     _plain_product_is_still_right(64, 512)
