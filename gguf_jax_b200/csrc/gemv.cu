@@ -1,6 +1,8 @@
 // ggq_gemv: argument checking and kernel selection for the small-batch fused multiply.
 #include "gemv.cuh"
 
+#include <cstdlib>
+
 using namespace ggq;
 
 namespace {
@@ -35,6 +37,10 @@ extern "C" size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32
   if (!ti || N <= 0 || K <= 0) return 0;
   size_t need = 0;
   if (qtype == QT_Q4_K || qtype == QT_Q5_K || qtype == QT_Q6_K) need = gemv_q4k_workspace_bytes(N, kMaxSmCount);
+  if (M <= kGemvMaxBatch) {
+    const size_t tile = gemv_tile_workspace_bytes(qtype, N, K, M < kTileMaxBatch ? M : kTileMaxBatch);
+    if (tile > need && K % 256 == 0) need = tile;
+  }
   if (M > kGemvMaxBatch && gemm_applicable(ti, N, K, M)) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess) { dev = -1; (void)cudaGetLastError(); }
@@ -82,7 +88,22 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
     else if (qtype == QT_Q5_K && gemv_q5k_applicable(N, K, 1, w, x_bf16)) tuned = gemv_q5k;
     else if (qtype == QT_Q6_K && gemv_q6k_applicable(N, K, 1, w, x_bf16)) tuned = gemv_q6k;
   }
-  if (tuned) {
+  static const bool q4k_m1_tiled = [] { const char* e = getenv("GGQ_Q4K_M1_TILED"); return e && e[0] == '1'; }();
+  const bool tile_first = qtype != QT_Q4_K || M > 1 || q4k_m1_tiled;    // Q4_K at batch 1 keeps its dedicated kernel
+  const size_t tile_need = gemv_tile_workspace_bytes(qtype, N, K, M < kTileMaxBatch ? M : kTileMaxBatch);
+  const bool tile_ok = tile_first && tile_need && workspace && workspace_bytes >= tile_need && (uintptr_t)workspace % 256 == 0 &&
+                       sm_count_of(dev) > 0 && gemv_tile_applicable(qtype, N, K, M < kTileMaxBatch ? M : kTileMaxBatch, w, x_bf16) &&
+                       (M <= kTileMaxBatch || ((K * 2) % 16 == 0));
+  if (tile_ok) {
+    // up to eight batch rows per launch; a larger batch reads the weight once per eight rows
+    err = cudaSuccess;
+    for (int m0 = 0; m0 < M && err == cudaSuccess; m0 += kTileMaxBatch) {
+      const int mb = M - m0 < kTileMaxBatch ? M - m0 : kTileMaxBatch;
+      err = gemv_tile(qtype, (const uint8_t*)w, N, K, (const uint8_t*)x_bf16 + (size_t)m0 * K * 2, mb,
+                      (uint8_t*)y + (size_t)m0 * N * y_item, y_dtype, workspace, workspace_bytes, sm_count_of(dev), nullptr, tab,
+                      st, nullptr);
+    }
+  } else if (tuned) {
     err = cudaSuccess;
     for (int m = 0; m < M && err == cudaSuccess; m++)
       err = tuned((const uint8_t*)w, N, K, (const uint8_t*)x_bf16 + (size_t)m * K * 2,

@@ -224,6 +224,14 @@ bool gemv_q5k_applicable(int64_t N, int64_t K, int M, const void* w, const void*
 cudaError_t gemv_q5k(const uint8_t* w, int64_t N, int64_t K, const void* x, void* y, int y_dtype, void* ws,
                      size_t ws_bytes, int sm_count, int* status, cudaStream_t st, const PeerPublish* peers = nullptr);
 
+// Tiled kernel for 1 <= M <= 8 (gemv_tile.cu): Q4_K, Q2_K, IQ4_XS and the IQ1/IQ2/IQ3 grid formats.
+bool gemv_tile_applicable(int qtype, int64_t N, int64_t K, int M, const void* w, const void* x);
+size_t gemv_tile_workspace_bytes(int qtype, int64_t N, int64_t K, int M);
+cudaError_t gemv_tile(int qtype, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y, int y_dtype,
+                      void* ws, size_t ws_bytes, int sm_count, int* status, const uint8_t* tab, cudaStream_t st,
+                      const PeerPublish* peers = nullptr);
+constexpr int kTileMaxBatch = 8;
+
 // Same kernel with the scratch in a file-scope device array (no caller buffer); returns a ggq_status.
 int32_t gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x, void* y, int32_t y_dtype,
                         int sm_count, cudaStream_t st);
