@@ -88,8 +88,9 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
     else if (qtype == QT_Q5_K && gemv_q5k_applicable(N, K, 1, w, x_bf16)) tuned = gemv_q5k;
     else if (qtype == QT_Q6_K && gemv_q6k_applicable(N, K, 1, w, x_bf16)) tuned = gemv_q6k;
   }
-  static const bool q4k_m1_tiled = [] { const char* e = getenv("GGQ_Q4K_M1_TILED"); return e && e[0] == '1'; }();
-  const bool tile_first = qtype != QT_Q4_K || M > 1 || q4k_m1_tiled;    // Q4_K at batch 1 keeps its dedicated kernel
+  static const bool m1_tiled = [] { const char* e = getenv("GGQ_Q4K_M1_TILED"); return e && e[0] == '1'; }();
+  const bool dedicated_m1 = qtype == QT_Q4_K || qtype == QT_Q5_K || qtype == QT_Q6_K;   // these keep their batch-1 kernels
+  const bool tile_first = !dedicated_m1 || M > 1 || m1_tiled;
   const size_t tile_need = gemv_tile_workspace_bytes(qtype, N, K, M < kTileMaxBatch ? M : kTileMaxBatch);
   const bool tile_ok = tile_first && tile_need && workspace && workspace_bytes >= tile_need && (uintptr_t)workspace % 256 == 0 &&
                        sm_count_of(dev) > 0 && gemv_tile_applicable(qtype, N, K, M < kTileMaxBatch ? M : kTileMaxBatch, w, x_bf16) &&

@@ -16,8 +16,12 @@
 // they are staged in shared memory.  A format provides
 //
 //   kTs, kQt            block bytes, qtype code
+//   kOct                octets per run: 8, or 16 for the two-plane formats (Q5_K, Q6_K), whose codes are
+//                       split into a nibble plane and a high-bit plane that are multiplied separately
+//                       (every weight then appears in two octets, with its activation staged twice)
 //   kGroupOct           octets per scale group inside a run (1, 2 or 4 = groups of 8, 16, 32)
-//   kSums               the fold needs the activations' sum per scale group
+//   kSums, kSumOct      the fold needs the activations' sum per scale group, taken over the group's first
+//                       kSumOct octets (all of them, or the first plane of a two-plane format)
 //   kPairOrder          0: an octet is 8 consecutive weights e..e+7 entering as (e, e+2), (e+1, e+3),
 //                          (e+4, e+6), (e+5, e+7)    [byte pairs (0,2), (1,3) of two words]
 //                       1: an octet is two quads a..a+3, b..b+3 entering as (a, a+1), (b, b+1),
@@ -44,10 +48,14 @@
 #include <stdint.h>
 #include <string.h>
 
+// Under nvcc everything here is device code (blocks and tables are addressed in shared memory);
+// a plain C++ compiler gets the same functions over ordinary memory for the host-side check.
 #if defined(__CUDACC__)
-#define TF_HD __host__ __device__ __forceinline__
+#define TF_HD __device__ __forceinline__
+#define TF_DEVICE 1
 #else
 #define TF_HD inline
+#define TF_DEVICE 0
 #endif
 
 namespace ggq {
@@ -55,7 +63,7 @@ namespace tf {
 
 // ---- small portable helpers -----------------------------------------------------------------
 TF_HD uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-#if defined(__CUDA_ARCH__)
+#if TF_DEVICE
   return __byte_perm(a, b, sel);
 #else
   const uint64_t v = (uint64_t)a | ((uint64_t)b << 32);
@@ -65,21 +73,21 @@ TF_HD uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 #endif
 }
 TF_HD uint32_t popc(uint32_t v) {
-#if defined(__CUDA_ARCH__)
+#if TF_DEVICE
   return __popc(v);
 #else
   return (uint32_t)__builtin_popcount(v);
 #endif
 }
 TF_HD uint32_t funnel16(uint32_t lo, uint32_t hi) {   // bytes 2..5 of the eight bytes (lo, hi)
-#if defined(__CUDA_ARCH__)
+#if TF_DEVICE
   return __funnelshift_r(lo, hi, 16);
 #else
   return (lo >> 16) | (hi << 16);
 #endif
 }
 TF_HD float f16_bits_to_float(uint32_t h) {
-#if defined(__CUDA_ARCH__)
+#if TF_DEVICE
   return __half2float(__ushort_as_half((unsigned short)h));
 #else
   const uint32_t s = (h >> 15) & 1, e = (h >> 10) & 31, m = h & 1023;
@@ -95,7 +103,7 @@ TF_HD float f16_bits_to_float(uint32_t h) {
 #endif
 }
 TF_HD float mulf(float a, float b) {
-#if defined(__CUDA_ARCH__)
+#if TF_DEVICE
   return __fmul_rn(a, b);
 #else
   volatile float r = a * b;
@@ -103,7 +111,7 @@ TF_HD float mulf(float a, float b) {
 #endif
 }
 TF_HD float fmaf_(float a, float b, float c) {
-#if defined(__CUDA_ARCH__)
+#if TF_DEVICE
   return __fmaf_rn(a, b, c);
 #else
   return __builtin_fmaf(a, b, c);
@@ -127,51 +135,67 @@ TF_HD uint32_t ksigns(uint32_t i7) { return i7 | ((popc(i7) & 1u) << 7); }
 // guarantees for that address (16, 8, 4: vector or word loads; 2: aligned word loads plus funnel
 // shifts when the address is 2 (mod 4) -- the branch is the same for every lane of a warp, since
 // rows start 16-byte aligned and all rows of a tile see the block at the same offset).
+// On the device a block lives in shared memory and is addressed by its 32-bit shared-window
+// address, so that field offsets fold into the load instructions.
+#if TF_DEVICE
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) { uint16_t v; asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint2 lds_v2(uint32_t a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
+__device__ __forceinline__ uint4 lds_v4(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
 struct BlockLd {
-  const uint8_t* p;
-  TF_HD uint32_t u16(int off) const { return *reinterpret_cast<const uint16_t*>(p + off); }
+  uint32_t p;        // shared-window address of the block's first byte
+  __device__ __forceinline__ uint32_t u16(int off) const { return lds_u16(p + off); }
   template <int NW, int A>
-  TF_HD void words(int off, uint32_t (&out)[NW]) const {
-#if defined(__CUDA_ARCH__)
-    const uint8_t* a = p + off;
+  __device__ __forceinline__ void words(int off, uint32_t (&out)[NW]) const {
+    const uint32_t a = p + off;
     if constexpr (A >= 16 && NW % 4 == 0) {
 #pragma unroll
       for (int i = 0; i < NW / 4; i++) {
-        const uint4 v = reinterpret_cast<const uint4*>(a)[i];
+        const uint4 v = lds_v4(a + 16 * i);
         out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
       }
     } else if constexpr (A >= 8 && NW % 2 == 0) {
 #pragma unroll
       for (int i = 0; i < NW / 2; i++) {
-        const uint2 v = reinterpret_cast<const uint2*>(a)[i];
+        const uint2 v = lds_v2(a + 8 * i);
         out[2 * i] = v.x; out[2 * i + 1] = v.y;
       }
     } else if constexpr (A >= 4) {
 #pragma unroll
-      for (int i = 0; i < NW; i++) out[i] = reinterpret_cast<const uint32_t*>(a)[i];
+      for (int i = 0; i < NW; i++) out[i] = lds_u32(a + 4 * i);
     } else {
-      if ((uintptr_t)a & 2) {
-        const uint32_t* q = reinterpret_cast<const uint32_t*>(a - 2);
-        uint32_t prev = q[0];
+      // 2-byte aligned: NW + 1 aligned words and a funnel shift by 0 or 16 bits (no branch: a branch
+      // here would leave the compiler unsure that the warp is converged at the next mma.sync)
+      const uint32_t base = a & ~3u, sh = (a & 2u) << 3;
+      uint32_t prev = lds_u32(base);
 #pragma unroll
-        for (int i = 0; i < NW; i++) { const uint32_t cur = q[i + 1]; out[i] = funnel16(prev, cur); prev = cur; }
-      } else {
-        const uint32_t* q = reinterpret_cast<const uint32_t*>(a);
-#pragma unroll
-        for (int i = 0; i < NW; i++) out[i] = q[i];
-      }
+      for (int i = 0; i < NW; i++) { const uint32_t cur = lds_u32(base + 4 + 4 * i); out[i] = __funnelshift_r(prev, cur, sh); prev = cur; }
     }
-#else
-    for (int i = 0; i < NW; i++) memcpy(&out[i], p + off + 4 * i, 4);
-#endif
   }
 };
-
-// Per-CTA lookup tables in shared memory (device) / plain memory (host check).
+// Per-CTA lookup tables in shared memory.
 struct Tables {
-  const uint8_t* grid;     // the format's grid, 8 (IQ1, IQ2) or 4 (IQ3) code bytes per entry
+  uint32_t grid;           // shared-window address of the format's grid: 8 (IQ1, IQ2) or 4 (IQ3) code bytes per entry
   uint32_t kv[4];          // IQ4_XS: the sixteen codes kvalues + 128, four per register
 };
+#else
+struct BlockLd {
+  const uint8_t* p;
+  uint32_t u16(int off) const { uint16_t v; memcpy(&v, p + off, 2); return v; }
+  template <int NW, int A>
+  void words(int off, uint32_t (&out)[NW]) const {
+    for (int i = 0; i < NW; i++) memcpy(&out[i], p + off + 4 * i, 4);
+  }
+};
+struct Tables {
+  const uint8_t* grid;
+  uint32_t kv[4];
+};
+#endif
 struct NoRun {};
 
 // =============================================================================================
@@ -180,7 +204,7 @@ struct NoRun {};
 // low-nibble sub-block, group 1 the high-nibble one (staged times 2^-4, the mask keeps the nibble
 // in place).  Contribution of a sub-block: (d * sc) * acc - (dmin * mn) * sum(x).
 struct Q4K {
-  static constexpr int kQt = 12, kTs = 144, kAlign = 16, kGroupOct = 4, kPairOrder = 0;
+  static constexpr int kQt = 12, kTs = 144, kAlign = 16, kOct = 8, kGroupOct = 4, kSumOct = 4, kPairOrder = 0;
   static constexpr bool kSums = true, kUnrollGroups = true;
   static constexpr int kTableBytes = 0;
   struct Run { uint32_t q[8]; float dl[2], ndm[2]; };
@@ -196,9 +220,9 @@ struct Q4K {
     // 6-bit scale / min of sub-blocks 2t, 2t+1: plain fields for t < 2, split fields for t >= 2
     const int sh = 16 * (t & 1);
     const uint32_t a = h[1] >> sh, m = h[2] >> sh, md = h[3] >> sh;
-    uint32_t scp, mnp;
-    if (t < 2) { scp = a & 0x3F3F; mnp = m & 0x3F3F; }
-    else { scp = (md & 0x0F0F) | ((a >> 2) & 0x3030); mnp = ((md >> 4) & 0x0F0F) | ((m >> 2) & 0x3030); }
+    const bool low = t < 2;       // selects, not a branch: the warp stays converged for the MMAs
+    const uint32_t scp = low ? (a & 0x3F3F) : ((md & 0x0F0F) | ((a >> 2) & 0x3030));
+    const uint32_t mnp = low ? (m & 0x3F3F) : (((md >> 4) & 0x0F0F) | ((m >> 2) & 0x3030));
     r.dl[0] = mulf(d, u2f(scp & 0xFF)); r.dl[1] = mulf(d, u2f(scp >> 8));
     r.ndm[0] = -mulf(dmin, u2f(mnp & 0xFF)); r.ndm[1] = -mulf(dmin, u2f(mnp >> 8));
     return r;
@@ -221,7 +245,7 @@ struct Q4K {
 // run t = (h, u) = (t >> 1, t & 1): the sixteen bytes qs[32 h + 16 u ..+16) at all four shifts;
 // group = shift s (16 weights, two octets = the two word pairs), staged times 2^-2s.
 struct Q2K {
-  static constexpr int kQt = 10, kTs = 84, kAlign = 4, kGroupOct = 2, kPairOrder = 0;
+  static constexpr int kQt = 10, kTs = 84, kAlign = 4, kOct = 8, kGroupOct = 2, kSumOct = 2, kPairOrder = 0;
   static constexpr bool kSums = true, kUnrollGroups = true;
   static constexpr int kTableBytes = 0;
   struct Run { uint32_t q[4]; uint32_t sc[4]; float d, ndmin; };
@@ -258,6 +282,107 @@ struct Q2K {
 };
 
 // =============================================================================================
+// Q5_K  (176 B: d, dmin, 12 packed 6-bit scales/mins, 32 bytes of fifth bits, 128 nibble bytes)
+// code = nibble | bit k of qh[p] << 4 for sub-block k, element p.  Two planes per sub-block: the
+// nibbles (as Q4_K) and the fifth bits, kept in place as qh & (0x00010001 << k) = bit * 2^k and
+// staged times 2^(4 - k), so that nibble and bit products add up in one accumulator to sum(code * x).
+// run t = sub-blocks 2t, 2t+1 = groups 0, 1 of eight octets: four of nibbles, four of fifth bits.
+struct Q5K {
+  static constexpr int kQt = 13, kTs = 176, kAlign = 16, kOct = 16, kGroupOct = 8, kSumOct = 4, kPairOrder = 0;
+  static constexpr bool kSums = true, kUnrollGroups = true;
+  static constexpr int kTableBytes = 0;
+  struct Run { uint32_t q[8], h[8]; float dl[2], ndm[2]; int t; };
+  struct Group { const Run* r; uint32_t mask_q, mask_h; float dl, ndm; };
+  TF_HD static void src_quads(int t, int oo, int& a, int& b) { a = 64 * t + 32 * (oo >> 3) + 8 * (oo & 3); b = a + 4; }
+  TF_HD static int x_exp(int t, int oo) {
+    const int k = 2 * t + (oo >> 3);
+    return (oo & 4) ? 4 - k : ((oo >> 3) ? -4 : 0);
+  }
+  TF_HD static Run load_run(const BlockLd& ld, int t) {
+    Run r;
+    uint32_t h[4];
+    ld.words<4, 16>(0, h);
+    ld.words<8, 16>(16, r.h);
+    ld.words<8, 16>(48 + 32 * t, r.q);
+    r.t = t;
+    const float d = f16_bits_to_float(h[0] & 0xFFFF), dmin = f16_bits_to_float(h[0] >> 16);
+    const int sh = 16 * (t & 1);
+    const uint32_t a = h[1] >> sh, m = h[2] >> sh, md = h[3] >> sh;
+    const bool low = t < 2;
+    const uint32_t scp = low ? (a & 0x3F3F) : ((md & 0x0F0F) | ((a >> 2) & 0x3030));
+    const uint32_t mnp = low ? (m & 0x3F3F) : (((md >> 4) & 0x0F0F) | ((m >> 2) & 0x3030));
+    r.dl[0] = mulf(d, u2f(scp & 0xFF)); r.dl[1] = mulf(d, u2f(scp >> 8));
+    r.ndm[0] = -mulf(dmin, u2f(mnp & 0xFF)); r.ndm[1] = -mulf(dmin, u2f(mnp >> 8));
+    return r;
+  }
+  TF_HD static Group load_group(const BlockLd&, const Run& r, int, int grp) {
+    return Group{&r, grp ? 0x00F000F0u : 0x000F000Fu, 0x00010001u << (2 * r.t + grp), r.dl[grp], r.ndm[grp]};
+  }
+  // octets 0-3: the nibbles of the sub-block, octets 4-7: its fifth bits (both add into one accumulator)
+  TF_HD static void octet(const Group& g, int q, const Tables&, uint32_t (&p)[4]) {
+    const uint32_t* w = q < 4 ? g.r->q : g.r->h;
+    const uint32_t m = q < 4 ? g.mask_q : g.mask_h;
+    const uint32_t w0 = w[2 * (q & 3)], w1 = w[2 * (q & 3) + 1];
+    p[0] = w0 & m; p[1] = (w0 >> 8) & m; p[2] = w1 & m; p[3] = (w1 >> 8) & m;
+  }
+  TF_HD static float fold(const Group& g, float acc, float xsum, float out) {
+    return fmaf_(g.ndm, xsum, fmaf_(g.dl, acc, out));
+  }
+};
+
+// =============================================================================================
+// Q6_K  (210 B: 128 low-nibble bytes, 64 bytes of 2-bit highs, 16 int8 scales, d)
+// element e = 128 h + 32 c + p: low = nibble (c >> 1) of ql[64 h + 32 (c & 1) + p], high = bits 2c, 2c+1 of
+// qh[32 h + p], weight = d * sc[8 h + 2 c + (p >> 4)] * (low + 16 high - 32).
+// run t = (h, u) = (t >> 1, t & 1): elements p in [16 u, 16 u + 16) of every c, i.e. four scale groups
+// of 16.  Two planes per group: the nibbles and the 2-bit highs kept in place (high * 4^c, staged times
+// 2^(4 - 2c)) add up in one accumulator to sum((low + 16 high) * x); group c = two octets of nibbles,
+// then two of highs.
+struct Q6K {
+  static constexpr int kQt = 14, kTs = 210, kAlign = 2, kOct = 16, kGroupOct = 4, kSumOct = 2, kPairOrder = 0;
+  static constexpr bool kSums = true, kUnrollGroups = true;
+  static constexpr int kTableBytes = 0;
+  struct Run { uint32_t qa[4], qb[4], qh[4]; float dl[4]; };
+  struct Group { const uint32_t* lo; const uint32_t* hi; uint32_t mask_lo, mask_hi; float dl; };
+  TF_HD static void src_quads(int t, int oo, int& a, int& b) {
+    a = 128 * (t >> 1) + 32 * (oo >> 2) + 16 * (t & 1) + 8 * (oo & 1);
+    b = a + 4;
+  }
+  TF_HD static int x_exp(int, int oo) {
+    const int c = oo >> 2;
+    return (oo & 2) ? 4 - 2 * c : ((c >> 1) ? -4 : 0);
+  }
+  TF_HD static Run load_run(const BlockLd& ld, int t) {
+    Run r;
+    const int h = t >> 1, u = t & 1;
+    ld.words<4, 2>(64 * h + 16 * u, r.qa);
+    ld.words<4, 2>(64 * h + 32 + 16 * u, r.qb);
+    ld.words<4, 2>(128 + 32 * h + 16 * u, r.qh);
+    uint32_t sc[2];
+    ld.words<2, 2>(192 + 8 * h, sc);
+    const float d = f16_bits_to_float(ld.u16(208));
+    for (int c = 0; c < 4; c++) {
+      const uint32_t byte = (sc[c >> 1] >> (16 * (c & 1) + 8 * u)) & 0xFF;
+      r.dl[c] = mulf(d, (float)(int)(int8_t)byte);
+    }
+    return r;
+  }
+  TF_HD static Group load_group(const BlockLd&, const Run& r, int, int grp) {
+    return Group{(grp & 1) ? r.qb : r.qa, r.qh, (grp >> 1) ? 0x00F000F0u : 0x000F000Fu, 0x00030003u << (2 * grp), r.dl[grp]};
+  }
+  // octets 0-1: the nibbles of the group's sixteen weights, octets 2-3: their 2-bit highs
+  TF_HD static void octet(const Group& g, int q, const Tables&, uint32_t (&p)[4]) {
+    const uint32_t* w = q < 2 ? g.lo : g.hi;
+    const uint32_t m = q < 2 ? g.mask_lo : g.mask_hi;
+    const uint32_t w0 = w[2 * (q & 1)], w1 = w[2 * (q & 1) + 1];
+    p[0] = w0 & m; p[1] = (w0 >> 8) & m; p[2] = w1 & m; p[3] = (w1 >> 8) & m;
+  }
+  TF_HD static float fold(const Group& g, float acc, float xsum, float out) {
+    return fmaf_(g.dl, fmaf_(-32.0f, xsum, acc), out);
+  }
+};
+
+// =============================================================================================
 // IQ4_XS  (136 B: d, scales_h, 4 scales_l bytes, 128 nibble bytes)
 // sub-block j (32 weights): low nibbles of qs[16 j ..+16) are weights 0-15, high nibbles 16-31;
 // weight = d * (ls - 32) * kvalues[nibble].  Codes are kvalues + 128 (1..241), looked up with byte
@@ -266,7 +391,7 @@ struct Q2K {
 // low nibbles (weights 4q..4q+3) and four high nibbles (16+4q..): MMA 1 takes the first two bytes
 // of the word, MMA 2 the last two (pair order 1).
 struct IQ4XS {
-  static constexpr int kQt = 23, kTs = 136, kAlign = 8, kGroupOct = 4, kPairOrder = 1;
+  static constexpr int kQt = 23, kTs = 136, kAlign = 8, kOct = 8, kGroupOct = 4, kSumOct = 4, kPairOrder = 1;
   static constexpr bool kSums = true, kUnrollGroups = false;
   static constexpr int kTableBytes = 0;
   typedef NoRun Run;
@@ -309,21 +434,18 @@ struct IQ4XS {
 // (IQ3) of unsigned code bytes, times eight sign bits.
 template <int ENTRY_BYTES>
 TF_HD void grid_words(const Tables& tb, uint32_t i0, uint32_t i1, uint32_t& w0, uint32_t& w1) {
+#if TF_DEVICE
   if (ENTRY_BYTES == 8) {
-#if defined(__CUDA_ARCH__)
-    const uint2 v = *reinterpret_cast<const uint2*>(tb.grid + 8 * i0);
+    const uint2 v = lds_v2(tb.grid + 8 * i0);
     w0 = v.x; w1 = v.y;
-#else
-    memcpy(&w0, tb.grid + 8 * i0, 4); memcpy(&w1, tb.grid + 8 * i0 + 4, 4);
-#endif
   } else {
-#if defined(__CUDA_ARCH__)
-    w0 = *reinterpret_cast<const uint32_t*>(tb.grid + 4 * i0);
-    w1 = *reinterpret_cast<const uint32_t*>(tb.grid + 4 * i1);
-#else
-    memcpy(&w0, tb.grid + 4 * i0, 4); memcpy(&w1, tb.grid + 4 * i1, 4);
-#endif
+    w0 = lds_u32(tb.grid + 4 * i0);
+    w1 = lds_u32(tb.grid + 4 * i1);
   }
+#else
+  if (ENTRY_BYTES == 8) { memcpy(&w0, tb.grid + 8 * i0, 4); memcpy(&w1, tb.grid + 8 * i0 + 4, 4); }
+  else { memcpy(&w0, tb.grid + 4 * i0, 4); memcpy(&w1, tb.grid + 4 * i1, 4); }
+#endif
 }
 TF_HD void signed_octet(uint32_t w0, uint32_t w1, uint32_t signs8, uint32_t (&p)[4]) {
   const uint32_t s0 = spread_signs4(signs8), s1 = spread_signs4(signs8 >> 4);
@@ -335,7 +457,7 @@ TF_HD void plain_octet(uint32_t w0, uint32_t w1, uint32_t (&p)[4]) {
 
 // IQ2_XXS (66 B: d, 8 x {4 index bytes, u32 = 4 x 7-bit sign index | 4-bit scale << 28}); group = one of them
 struct IQ2XXS {
-  static constexpr int kQt = 16, kTs = 66, kAlign = 2, kGroupOct = 4, kPairOrder = 0;
+  static constexpr int kQt = 16, kTs = 66, kAlign = 2, kOct = 8, kGroupOct = 4, kSumOct = 4, kPairOrder = 0;
   static constexpr bool kSums = false, kUnrollGroups = false;
   static constexpr int kTableBytes = 256 * 8;
   typedef NoRun Run;
@@ -359,7 +481,7 @@ struct IQ2XXS {
 
 // IQ2_XS (74 B: d, 32 x u16 = 9-bit grid index | 7-bit sign index << 9, 8 scale bytes of two nibbles)
 struct IQ2XS {
-  static constexpr int kQt = 17, kTs = 74, kAlign = 2, kGroupOct = 2, kPairOrder = 0;
+  static constexpr int kQt = 17, kTs = 74, kAlign = 2, kOct = 8, kGroupOct = 2, kSumOct = 2, kPairOrder = 0;
   static constexpr bool kSums = false, kUnrollGroups = false;
   static constexpr int kTableBytes = 512 * 8;
   typedef NoRun Run;
@@ -385,7 +507,7 @@ struct IQ2XS {
 
 // IQ2_S (82 B: d, 32 index bytes, 32 sign bytes, 8 bytes of 2 high index bits, 8 scale bytes)
 struct IQ2S {
-  static constexpr int kQt = 22, kTs = 82, kAlign = 2, kGroupOct = 2, kPairOrder = 0;
+  static constexpr int kQt = 22, kTs = 82, kAlign = 2, kOct = 8, kGroupOct = 2, kSumOct = 2, kPairOrder = 0;
   static constexpr bool kSums = false, kUnrollGroups = false;
   static constexpr int kTableBytes = 1024 * 8;
   typedef NoRun Run;
@@ -413,7 +535,7 @@ struct IQ2S {
 
 // IQ3_XXS (98 B: d, 64 index bytes (one per 4 weights), 8 x u32 = 4 x 7-bit sign index | scale << 28)
 struct IQ3XXS {
-  static constexpr int kQt = 18, kTs = 98, kAlign = 2, kGroupOct = 4, kPairOrder = 0;
+  static constexpr int kQt = 18, kTs = 98, kAlign = 2, kOct = 8, kGroupOct = 4, kSumOct = 4, kPairOrder = 0;
   static constexpr bool kSums = false, kUnrollGroups = false;
   static constexpr int kTableBytes = 256 * 4;
   typedef NoRun Run;
@@ -441,7 +563,7 @@ struct IQ3XXS {
 
 // IQ3_S (110 B: d, 64 index bytes, 8 bytes of ninth index bits, 32 sign bytes, 4 scale bytes of two nibbles)
 struct IQ3S {
-  static constexpr int kQt = 21, kTs = 110, kAlign = 2, kGroupOct = 4, kPairOrder = 0;
+  static constexpr int kQt = 21, kTs = 110, kAlign = 2, kOct = 8, kGroupOct = 4, kSumOct = 4, kPairOrder = 0;
   static constexpr bool kSums = false, kUnrollGroups = false;
   static constexpr int kTableBytes = 512 * 4;
   typedef NoRun Run;
@@ -476,7 +598,7 @@ struct IQ3S {
 // holds the codes 8 grid + 9 (1, 9, 17); adding or subtracting 1 in every byte applies delta, the
 // fold removes the 9 and the factor 8:  (dl / 8) * (sum(code x) - 9 sum(x)).
 struct IQ1S {
-  static constexpr int kQt = 19, kTs = 50, kAlign = 2, kGroupOct = 4, kPairOrder = 0;
+  static constexpr int kQt = 19, kTs = 50, kAlign = 2, kOct = 8, kGroupOct = 4, kSumOct = 4, kPairOrder = 0;
   static constexpr bool kSums = true, kUnrollGroups = false;
   static constexpr int kTableBytes = 2048 * 8;
   typedef NoRun Run;
@@ -506,7 +628,7 @@ struct IQ1S {
 // IQ1_M (56 B: 32 index bytes, 16 bytes of 2 x {3 high index bits, delta sign}, 4 x u16 = 4 x 3-bit scale |
 // a nibble of the f16 super-scale << 12)
 struct IQ1M {
-  static constexpr int kQt = 29, kTs = 56, kAlign = 8, kGroupOct = 2, kPairOrder = 0;
+  static constexpr int kQt = 29, kTs = 56, kAlign = 8, kOct = 8, kGroupOct = 2, kSumOct = 2, kPairOrder = 0;
   static constexpr bool kSums = true, kUnrollGroups = false;
   static constexpr int kTableBytes = 2048 * 8;
   typedef NoRun Run;

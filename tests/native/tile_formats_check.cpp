@@ -47,45 +47,47 @@ int check(const std::vector<uint8_t>& blocks, const float* want, const Tables& t
     ld = BlockLd{p};
     for (int t = 0; t < 4; t++) {
       const typename F::Run run = F::load_run(ld, t);
-      for (int grp = 0; grp < 8 / F::kGroupOct; grp++) {
+      for (int grp = 0; grp < F::kOct / F::kGroupOct; grp++) {
         const typename F::Group raw = F::load_group(ld, run, t, grp);
-        // one-hot activations: x = 1 at one weight of the group, 0 elsewhere, for every weight
+        // one-hot activations, one weight at a time: the group's accumulator receives code * x from every
+        // octet the weight appears in (one, or one per plane), the sum of x is 1
+        std::vector<double> acc(256, 0.0);
+        std::vector<int> in_group(256, 0), in_sum(256, 0);
         for (int oo = grp * F::kGroupOct; oo < (grp + 1) * F::kGroupOct; oo++) {
           uint32_t pr[4];
           F::octet(raw, oo - grp * F::kGroupOct, tb, pr);
           int qa, qb;
           F::src_quads(t, oo, qa, qb);
           const double xs = std::ldexp(1.0, F::x_exp(t, oo));    // staged activations carry this factor
-          int e[8];
-          double c[8];
           for (int m = 0; m < 2; m++) {          // MMA m: registers pr[2m] (k-slots 2t, 2t+1), pr[2m+1] (2t+8, 2t+9)
             for (int h = 0; h < 2; h++) {
               const uint32_t reg = pr[2 * m + h];
-              const int v = 4 * m + 2 * h;
-              c[v] = code_of(reg & 0xFFFF);
-              c[v + 1] = code_of(reg >> 16);
-              if (F::kPairOrder == 0) { e[v] = (m ? qb : qa) + h; e[v + 1] = (m ? qb : qa) + h + 2; }
-              else { e[v] = (h ? qb : qa) + 2 * m; e[v + 1] = (h ? qb : qa) + 2 * m + 1; }
+              int e0, e1;
+              if (F::kPairOrder == 0) { e0 = (m ? qb : qa) + h; e1 = e0 + 2; }
+              else { e0 = (h ? qb : qa) + 2 * m; e1 = e0 + 1; }
+              acc[e0] += code_of(reg & 0xFFFF) * xs;
+              acc[e1] += code_of(reg >> 16) * xs;
+              in_group[e0]++; in_group[e1]++;
+              if (oo - grp * F::kGroupOct < F::kSumOct) { in_sum[e0]++; in_sum[e1]++; }
+              cover[e0]++; cover[e1]++;
             }
           }
-          for (int v = 0; v < 8; v++) {
-            cover[e[v]]++;
-            // acc = code * (1 * 2^x_exp), xsum = 1 (the sums are taken over the unscaled activations)
-            const float got = F::fold(raw, (float)(c[v] * xs), 1.0f, 0.0f);
-            const float ref = want[(size_t)b * 256 + e[v]];
-            seen++;
-            if (!(got == ref) && !(std::isnan(got) && std::isnan(ref))) {
-              if (bad < 10)
-                fprintf(stderr, "block %d run %d octet %d value %d (weight %d): got %.9g want %.9g\n", b, t, oo, v, e[v],
-                        got, ref);
-              bad++;
-            }
+        }
+        for (int e = 0; e < 256; e++) {
+          if (!in_group[e]) continue;
+          if (in_sum[e] != 1) { fprintf(stderr, "weight %d enters the group's sum of x %d times\n", e, in_sum[e]); return 1; }
+          const float got = F::fold(raw, (float)acc[e], 1.0f, 0.0f);
+          const float ref = want[(size_t)b * 256 + e];
+          seen++;
+          if (!(got == ref) && !(std::isnan(got) && std::isnan(ref))) {
+            if (bad < 10) fprintf(stderr, "block %d run %d group %d weight %d: got %.9g want %.9g\n", b, t, grp, e, got, ref);
+            bad++;
           }
         }
       }
     }
     for (int i = 0; i < 256; i++)
-      if (cover[i] != 1) { fprintf(stderr, "block %d: weight %d covered %d times\n", b, i, cover[i]); return 1; }
+      if (cover[i] != F::kOct / 8) { fprintf(stderr, "block %d: weight %d covered %d times\n", b, i, cover[i]); return 1; }
   }
   printf("qtype %d: %ld values checked, %ld mismatches\n", F::kQt, seen, bad);
   return bad ? 1 : 0;
@@ -102,6 +104,8 @@ int main(int argc, char** argv) {
   switch (qt) {
     case Q4K::kQt: return check<Q4K>(blocks, want, tb, nb);
     case Q2K::kQt: return check<Q2K>(blocks, want, tb, nb);
+    case Q5K::kQt: return check<Q5K>(blocks, want, tb, nb);
+    case Q6K::kQt: return check<Q6K>(blocks, want, tb, nb);
     case IQ4XS::kQt: return check<IQ4XS>(blocks, want, tb, nb);
     case IQ2XXS::kQt: return check<IQ2XXS>(blocks, want, tb, nb);
     case IQ2XS::kQt: return check<IQ2XS>(blocks, want, tb, nb);

@@ -14,7 +14,7 @@ from oracle import oracle as O
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SRC = os.path.join(ROOT, "tests", "native", "tile_formats_check.cpp")
-TILE_QTYPES = [QT.Q4_K, QT.Q2_K, QT.IQ4_XS, QT.IQ2_XXS, QT.IQ2_XS, QT.IQ2_S, QT.IQ3_XXS, QT.IQ3_S, QT.IQ1_S, QT.IQ1_M]
+TILE_QTYPES = [QT.Q4_K, QT.Q5_K, QT.Q6_K, QT.Q2_K, QT.IQ4_XS, QT.IQ2_XXS, QT.IQ2_XS, QT.IQ2_S, QT.IQ3_XXS, QT.IQ3_S, QT.IQ1_S, QT.IQ1_M]
 _TAB_OFFSET = {QT.IQ2_XXS: (0, 2048), QT.IQ2_XS: (2048, 4096), QT.IQ2_S: (6144, 8192), QT.IQ3_XXS: (14336, 1024),
                QT.IQ3_S: (15360, 2048), QT.IQ1_S: (17408, 16384), QT.IQ1_M: (17408, 16384)}
 
