@@ -38,7 +38,8 @@ extern "C" size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32
   size_t need = 0;
   if (qtype == QT_Q4_K || qtype == QT_Q5_K || qtype == QT_Q6_K) need = gemv_q4k_workspace_bytes(N, kMaxSmCount);
   if (M <= kGemvMaxBatch) {
-    const size_t tile = gemv_tile_workspace_bytes(qtype, N, K, M < kTileMaxBatch ? M : kTileMaxBatch);
+    const int tmax = gemv_tile_max_batch(qtype);
+    const size_t tile = tmax ? gemv_tile_workspace_bytes(qtype, N, K, M < tmax ? M : tmax) : 0;
     if (tile > need && K % 256 == 0) need = tile;
   }
   if (M > kGemvMaxBatch && gemm_applicable(ti, N, K, M)) {
@@ -91,15 +92,16 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
   static const bool m1_tiled = [] { const char* e = getenv("GGQ_Q4K_M1_TILED"); return e && e[0] == '1'; }();
   const bool dedicated_m1 = qtype == QT_Q4_K || qtype == QT_Q5_K || qtype == QT_Q6_K;   // these keep their batch-1 kernels
   const bool tile_first = !dedicated_m1 || M > 1 || m1_tiled;
-  const size_t tile_need = gemv_tile_workspace_bytes(qtype, N, K, M < kTileMaxBatch ? M : kTileMaxBatch);
+  const int tile_max = gemv_tile_max_batch(qtype);
+  const int tile_m = M < tile_max ? M : tile_max;
+  const size_t tile_need = tile_max ? gemv_tile_workspace_bytes(qtype, N, K, tile_m) : 0;
   const bool tile_ok = tile_first && tile_need && workspace && workspace_bytes >= tile_need && (uintptr_t)workspace % 256 == 0 &&
-                       sm_count_of(dev) > 0 && gemv_tile_applicable(qtype, N, K, M < kTileMaxBatch ? M : kTileMaxBatch, w, x_bf16) &&
-                       (M <= kTileMaxBatch || ((K * 2) % 16 == 0));
+                       sm_count_of(dev) > 0 && gemv_tile_applicable(qtype, N, K, tile_m, w, x_bf16);
   if (tile_ok) {
-    // up to eight batch rows per launch; a larger batch reads the weight once per eight rows
+    // up to tile_max batch rows per launch; a larger batch reads the weight once per tile_max rows
     err = cudaSuccess;
-    for (int m0 = 0; m0 < M && err == cudaSuccess; m0 += kTileMaxBatch) {
-      const int mb = M - m0 < kTileMaxBatch ? M - m0 : kTileMaxBatch;
+    for (int m0 = 0; m0 < M && err == cudaSuccess; m0 += tile_max) {
+      const int mb = M - m0 < tile_max ? M - m0 : tile_max;
       err = gemv_tile(qtype, (const uint8_t*)w, N, K, (const uint8_t*)x_bf16 + (size_t)m0 * K * 2, mb,
                       (uint8_t*)y + (size_t)m0 * N * y_item, y_dtype, workspace, workspace_bytes, sm_count_of(dev), nullptr, tab,
                       st, nullptr);

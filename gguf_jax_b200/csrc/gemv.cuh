@@ -230,7 +230,7 @@ size_t gemv_tile_workspace_bytes(int qtype, int64_t N, int64_t K, int M);
 cudaError_t gemv_tile(int qtype, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y, int y_dtype,
                       void* ws, size_t ws_bytes, int sm_count, int* status, const uint8_t* tab, cudaStream_t st,
                       const PeerPublish* peers = nullptr);
-constexpr int kTileMaxBatch = 8;
+int gemv_tile_max_batch(int qtype);     // batch rows per launch (8, Q6_K: 4; 0 if qtype has no tile format)
 
 // Same kernel with the scratch in a file-scope device array (no caller buffer); returns a ggq_status.
 int32_t gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x, void* y, int32_t y_dtype,

@@ -58,7 +58,7 @@ struct Geo {
   int depth, pitch, slot_bytes;
   int xbufs;             // chunk buffers: the most adjacent chunks the warps of one CTA touch
   int x_rows;            // staged batch rows = 2 * passes (rows >= M are zero)
-  int x_row_bytes;       // chunk_sb * 64 * octets per run
+  int x_row_bytes;       // staged bytes per batch row and chunk, padded to 64 (mod 128)
   int xs_row_floats;     // sums per batch row and chunk
   int off_x, off_xs, off_zero, off_tab, off_misc, total;
 };
@@ -92,6 +92,65 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&p);
 }
 __device__ __forceinline__ float lds_f32(uint32_t a) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a)); return v; }
+
+// ---- Q4_K at batch 1 and 2: one B register set serves the low- and the high-nibble MMA of a word.
+// Lane g = 2t of a quad's column pair reads the activations of sub-block 2t, lane g = 2t + 1 those of
+// sub-block 2t + 1 (staged times 2^-4); column 2t of the low-nibble accumulator and column 2t + 1 of the
+// high-nibble accumulator are the two sub-block sums, the other two columns are not used.
+// byte `SEL` (0..3) of x as a float, exact: bits 0x4B0000vv are 2^23 + v.
+template <int SEL>
+__device__ __forceinline__ float byte_to_float(uint32_t x) {
+  return __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7440 + SEL)) - 8388608.0f;
+}
+struct Q4kLane {          // per-lane constants of the 6-bit scale unpack (t < 2: plain fields, else split fields)
+  bool low;
+  int sh, sh2, shm;
+  uint32_t ma, mb;
+  __device__ explicit Q4kLane(int t)
+      : low(t < 2), sh(16 * (t & 1)), sh2(16 * (t & 1) + 2), shm(16 * (t & 1) + (t < 2 ? 0 : 4)),
+        ma(t < 2 ? 0x3F3Fu : 0x0F0Fu), mb(t < 2 ? 0u : 0x3030u) {}
+};
+__device__ __forceinline__ void q4k_pair_scales(const uint4& h, const Q4kLane& c, float& dl_a, float& ndm_a, float& dl_b,
+                                                float& ndm_b) {
+  const __half2 dd = *reinterpret_cast<const __half2*>(&h.x);
+  const float d = __low2float(dd), ndmin = -__high2float(dd);
+  const uint32_t a_sc = c.low ? h.y : h.w, a_mn = c.low ? h.z : h.w;
+  const uint32_t scp = ((a_sc >> c.sh) & c.ma) | ((h.y >> c.sh2) & c.mb);
+  const uint32_t mnp = ((a_mn >> c.shm) & c.ma) | ((h.z >> c.sh2) & c.mb);
+  dl_a = __fmul_rn(d, byte_to_float<0>(scp));
+  dl_b = __fmul_rn(d, byte_to_float<1>(scp));
+  ndm_a = __fmul_rn(ndmin, byte_to_float<0>(mnp));
+  ndm_b = __fmul_rn(ndmin, byte_to_float<1>(mnp));
+}
+// One superblock of 16 rows: blk0 / blk1 = shared addresses of the block in rows g / g + 8, xa = this
+// lane's 64 bytes of activations (or the zero page, step 0), xsa = the two sub-block sums of x.
+__device__ __forceinline__ void q4k_block_m1(uint32_t blk0, uint32_t blk1, int t, const Q4kLane& lc, uint32_t xa, uint32_t x_step,
+                                             uint32_t xsa, float& out0, float& out1) {
+  const uint4 h0 = tf::lds_v4(blk0), h1 = tf::lds_v4(blk1);
+  const uint4 qa0 = tf::lds_v4(blk0 + 16 + 32 * t), qb0 = tf::lds_v4(blk0 + 32 + 32 * t);
+  const uint4 qa1 = tf::lds_v4(blk1 + 16 + 32 * t), qb1 = tf::lds_v4(blk1 + 32 + 32 * t);
+  const uint4 x0 = tf::lds_v4(xa), x1 = tf::lds_v4(xa + x_step), x2 = tf::lds_v4(xa + 2 * x_step), x3 = tf::lds_v4(xa + 3 * x_step);
+  const uint2 sxu = tf::lds_v2(xsa);
+  const float sx0 = __uint_as_float(sxu.x), sx1 = __uint_as_float(sxu.y);
+  float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t w0[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qb0.x, qb0.y, qb0.z, qb0.w};
+  const uint32_t w1[8] = {qa1.x, qa1.y, qa1.z, qa1.w, qb1.x, qb1.y, qb1.z, qb1.w};
+  const uint32_t xr[16] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w, x2.x, x2.y, x2.z, x2.w, x3.x, x3.y, x3.z, x3.w};
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const uint32_t a = w0[i], b = w1[i];
+    const uint32_t as = a >> 8, bs = b >> 8;
+    mma16816(lo, a & 0x000F000Fu, b & 0x000F000Fu, as & 0x000F000Fu, bs & 0x000F000Fu, xr[2 * i], xr[2 * i + 1]);
+    mma16816(hi, a & 0x00F000F0u, b & 0x00F000F0u, as & 0x00F000F0u, bs & 0x00F000F0u, xr[2 * i], xr[2 * i + 1]);
+  }
+  float dla, dma, dlb, dmb;
+  q4k_pair_scales(h0, lc, dla, dma, dlb, dmb);
+  out0 = fmaf(dla, lo[0], out0); out0 = fmaf(dma, sx0, out0);
+  out0 = fmaf(dlb, hi[1], out0); out0 = fmaf(dmb, sx1, out0);
+  q4k_pair_scales(h1, lc, dla, dma, dlb, dmb);
+  out1 = fmaf(dla, lo[2], out1); out1 = fmaf(dma, sx0, out1);
+  out1 = fmaf(dlb, hi[3], out1); out1 = fmaf(dmb, sx1, out1);
+}
 
 template <class F, int MP>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -216,6 +275,8 @@ gemv_tile_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat1
 
   // Stage the activations of chunk c into buffer cb: destination order [block][run t][octet][8 values],
   // 16 bytes per octet, so a lane's run of a block is 128 contiguous bytes.
+  constexpr uint32_t kRunBytes = F::kOct * 16;          // staged activations of one lane run
+  constexpr uint32_t kRunStride = kRunBytes + 16;
   auto stage_pass = [&](int cb, int c, int m, int S) -> float {
     const int n_oct = geo.chunk_sb * (4 * F::kOct);
     uint4* xv = reinterpret_cast<uint4*>(smem + geo.off_x + (cb * XR + m) * geo.x_row_bytes);
@@ -246,7 +307,9 @@ gemv_tile_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat1
                                                pack_bf16(b0 * up, b2 * up), pack_bf16(b1 * up, b3 * up));
       else o4 = make_uint4(pack_bf16(a0 * up, a1 * up), pack_bf16(b0 * up, b1 * up),
                            pack_bf16(a2 * up, a3 * up), pack_bf16(b2 * up, b3 * up));
-      xv[o] = o4;
+      // a run takes kRunBytes + 16 bytes and a batch row 64 (mod 128) bytes, so that the eight lanes that
+      // read activations at once (four runs x two batch rows) hit eight different 16-byte bank groups
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(xv) + (blk * 4 + tt) * kRunStride + oo * 16) = o4;
       float sum = ((a0 + a1) + (a2 + a3)) + ((b0 + b1) + (b2 + b3));
       const float asum = ((fabsf(a0) + fabsf(a1)) + (fabsf(a2) + fabsf(a3))) + ((fabsf(b0) + fabsf(b1)) + (fabsf(b2) + fabsf(b3)));
       amax = fmaxf(amax, asum);
@@ -281,9 +344,8 @@ gemv_tile_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat1
 
   const bool live = (g >> 1) == t;
   const uint32_t zero_addr = smem_base + geo.off_zero;
-  constexpr uint32_t kRunBytes = F::kOct * 16;          // staged activations of one lane run
-  const uint32_t x_lane = live ? smem_base + geo.off_x + (g & 1) * geo.x_row_bytes + t * kRunBytes : zero_addr;
-  const uint32_t x_pass = live ? 2u * geo.x_row_bytes : 0u, x_oct = live ? 16u : 0u, x_blk = live ? 4u * kRunBytes : 0u;
+  const uint32_t x_lane = live ? smem_base + geo.off_x + (g & 1) * geo.x_row_bytes + t * kRunStride : zero_addr;
+  const uint32_t x_pass = live ? 2u * geo.x_row_bytes : 0u, x_oct = live ? 16u : 0u, x_blk = live ? 4u * kRunStride : 0u;
   const uint32_t x_buf = live ? (uint32_t)(XR * geo.x_row_bytes) : 0u;
   const uint32_t xs_base = smem_base + geo.off_xs;
   constexpr int kGroups = F::kOct / F::kGroupOct;
@@ -321,6 +383,12 @@ gemv_tile_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat1
     pend_rt = -1;
   };
 
+  // Q4_K at batch 1: the dedicated inner loop (see q4k_block_m1); everything else takes the generic one
+  constexpr bool kQ4kM1 = F::kQt == QT_Q4_K && MP == 1;
+  const bool q4k_fast = kQ4kM1 && M == 1;
+  const Q4kLane q4k_lane(t);
+  const uint32_t q4k_x_lane = live ? smem_base + geo.off_x + t * kRunStride + (g & 1) * 64 : zero_addr;
+
   if (active) {
     int c = c0, rt = rt0, k = k0, slot = 0, seg_k = k0;
     float out[MP][4];
@@ -336,7 +404,16 @@ gemv_tile_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat1
       const uint32_t tile = my_ring + slot * geo.slot_bytes + g * pitch + ((sb0 * F::kTs) & 15);
       const uint32_t xr0 = x_lane + cb * x_buf + (k * nb) * x_blk;
       const uint32_t xs0 = xs_base + (uint32_t)(((cb * XR) * geo.xs_row_floats + (k * nb * 4 + t) * kGroups) * 4);
-      for (int blk = 0; blk < nbh; blk++) {
+      if constexpr (kQ4kM1) {
+        if (q4k_fast) {
+          const uint32_t xa0 = q4k_x_lane + cb * x_buf + (k * nb) * x_blk;
+          const uint32_t xsa0 = xs0;           // the run's two sub-block sums: xs[(blk * 4 + t) * 2 + {0, 1}]
+          for (int blk = 0; blk < nbh; blk++)
+            q4k_block_m1(tile + blk * F::kTs, tile + blk * F::kTs + 8 * pitch, t, q4k_lane, xa0 + blk * x_blk, x_oct,
+                         xsa0 + blk * (4 * kGroups * 4), out[0][0], out[0][2]);
+        }
+      }
+      for (int blk = 0; blk < (q4k_fast ? 0 : nbh); blk++) {
         const tf::BlockLd ld0{tile + blk * F::kTs}, ld1{tile + blk * F::kTs + 8 * pitch};
         const typename F::Run run0 = F::load_run(ld0, t), run1 = F::load_run(ld1, t);
         const uint32_t xr = xr0 + blk * x_blk;
@@ -508,7 +585,8 @@ static bool plan(const FormatInfo& fi, int64_t N, int64_t K, int M, int sm_count
         const int64_t units = (int64_t)g.C * g.RT;
         g.W = (int)std::min<int64_t>((int64_t)sm_count * kWarps, units);
         g.x_rows = x_rows;
-        g.x_row_bytes = g.chunk_sb * 64 * fi.oct;
+        g.x_row_bytes = g.chunk_sb * 4 * (16 * fi.oct + 16);
+        g.x_row_bytes += (64 - g.x_row_bytes % 128 + 128) % 128;      // 64 (mod 128): see the staging
         g.xs_row_floats = fi.sums ? g.chunk_sb * 4 * fi.sum_groups : 0;
         const int pieces = (14 + nb * fi.ts + 15) / 16;
         g.pitch = 16 * pieces;
@@ -583,10 +661,18 @@ static cudaError_t launch_passes(int MP, const Geo& geo, int grid, cudaStream_t 
 
 }  // namespace tile
 
+// Most batch rows one launch takes for qtype (0: not a tile format).  Four passes only pay where decoding
+// dominates; Q6_K, with two planes and 32 MMAs per block and pass, is faster as two launches of two passes.
+int gemv_tile_max_batch(int qtype) {
+  tile::FormatInfo fi;
+  if (!tile::format_of(qtype, &fi)) return 0;
+  return qtype == QT_Q6_K ? 4 : tile::kMaxBatch;
+}
+
 bool gemv_tile_applicable(int qtype, int64_t N, int64_t K, int M, const void* w, const void* x) {
   tile::FormatInfo fi;
   if (!tile::format_of(qtype, &fi)) return false;
-  if (M < 1 || M > tile::kMaxBatch || K <= 0 || K % 256 || N < 1 || N > (1ll << 24)) return false;
+  if (M < 1 || M > gemv_tile_max_batch(qtype) || K <= 0 || K % 256 || N < 1 || N > (1ll << 24)) return false;
   if ((K / 256 * fi.ts) % 16 || (uintptr_t)w % 16 || (uintptr_t)x % 16 || (K * 2) % 16) return false;
   if (N * (K / 256 * fi.ts) >= (1ll << 31)) return false;      // block offsets are 32-bit inside a row; rows are 64-bit
   tile::Geo geo;
