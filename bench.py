@@ -351,6 +351,152 @@ def decode_leg(world: int, rank: int, dev) -> dict:
                     "magnitude; one CUDA graph per token"}
 
 
+# ---------------------------------------------------------------------------------------------
+# Other configurations of the workload family, measured on one GPU next to the headline (own keys in
+# the JSON line, outside the headline's timed region).
+
+LOWBIT_SWEEP = ["Q2_K", "IQ1_S", "IQ1_M", "IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ4_XS"]
+LLAMA_1B_LAYER = [("q", "Q4_K", 2048, 2048), ("k", "Q4_K", 512, 2048), ("v", "Q6_K", 512, 2048), ("o", "Q4_K", 2048, 2048),
+                  ("gate", "Q4_K", 8192, 2048), ("up", "Q4_K", 8192, 2048), ("down", "Q6_K", 2048, 8192)]
+LLAMA_8B_SHAPES = [("attn_q", "Q5_K", 4096, 4096), ("attn_k", "Q5_K", 1024, 4096), ("ffn_gate", "Q6_K", 14336, 4096),
+                   ("ffn_down", "Q6_K", 4096, 14336)]
+
+
+def _graph_us(calls, repeats: int = 5) -> float:
+    """Median microseconds per call of a list of zero-argument launches, replayed as one CUDA graph."""
+    import torch
+    for f in calls:
+        f()
+    torch.cuda.synchronize()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for f in calls:
+                f()
+    ts = []
+    for _ in range(repeats + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(st):
+            e0.record(st)
+            g.replay()
+            e1.record(st)
+        st.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3 / len(calls))
+    del g
+    return float(statistics.median(ts[1:]))
+
+
+def extra_legs(dev) -> dict:
+    import numpy as np
+    import torch
+    from gguf.constants import GGML_QUANT_SIZES
+    from gguf.constants import GGMLQuantizationType as QT
+
+    import gguf_jax_b200 as gj
+    from gguf_jax_b200 import kernels, synth
+    from oracle import oracle as O
+
+    peak, _ = measured_peak()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            tf_peak = float(json.load(f)["bf16_tflops_sustained"])
+    except Exception:  # noqa: BLE001
+        tf_peak = 1400.0
+
+    def wbytes(qt, n, k):
+        bs, ts = GGML_QUANT_SIZES[qt]
+        return n * (k // bs) * ts
+
+    def x_of(m, k, seed=0):
+        return torch.from_numpy(synth.make_x(m, k, seed=seed)).to(dev).to(torch.bfloat16)
+
+    def sampled_parity(x, w, y, rows=64):
+        pick = np.sort(np.random.default_rng(3).choice(w.shape[0], size=min(rows, w.shape[0]), replace=False))
+        ref = O.c_matmul(O.bf16_bits(x.float().cpu().numpy()), w.data[torch.from_numpy(pick).to(dev)].cpu().numpy(), w.qtype)
+        return O.rel_l2(y.float()[:, torch.from_numpy(pick).to(dev)].cpu().numpy(), ref)
+
+    out = {}
+
+    # ---- the low-bit sweep: nine qtypes on 8192 x 28672 at batch 1, 4, 8
+    sweep = {}
+    for name in LOWBIT_SWEEP:
+        qt = QT[name]
+        nbytes = wbytes(qt, N_ROWS, K_DIM)
+        copies = max(3, -(-300_000_000 // nbytes))
+        ws = [synth.make_weight_on_device(N_ROWS, K_DIM, qt, seed=40 + c, device=dev) for c in range(copies)]
+        row = {}
+        for m in (1, 4, 8):
+            x = x_of(m, K_DIM, m)
+            us = _graph_us([(lambda w=w: kernels.fused_matmul(x, w)) for w in ws * 2])
+            moved = nbytes + 2 * m * K_DIM + 2 * m * N_ROWS
+            row[f"m{m}"] = {"us": us, "gbs": moved / us / 1e3, "frac_of_measured_hbm": moved / us / 1e3 / peak}
+        x = x_of(4, K_DIM, 4)
+        row["rel_l2_sampled_rows_m4"] = sampled_parity(x, ws[0], kernels.fused_matmul(x, ws[0], out_dtype=torch.float32))
+        sweep[name] = row
+        del ws
+        torch.cuda.empty_cache()
+    out["lowbit_sweep_8192x28672"] = sweep
+
+    # ---- Llama-3.2-1B-shaped decode layer (Q4_K with attn_v / ffn_down in Q6_K), a 16-layer stack per batch
+    layers = [[synth.make_weight_on_device(n, k, QT[q], seed=1000 + 10 * li + i, device=dev)
+               for i, (_, q, n, k) in enumerate(LLAMA_1B_LAYER)] for li in range(16)]
+    layer_bytes = sum(wbytes(QT[q], n, k) for _, q, n, k in LLAMA_1B_LAYER)
+    stack = {}
+    for m in (1, 2, 4, 8, 16):
+        xs = {k: x_of(m, k, m) for k in (2048, 8192)}
+        calls = [(lambda w=w: kernels.fused_matmul(xs[w.shape[1]], w)) for ws in layers for w in ws]
+        us_layer = _graph_us(calls) * len(LLAMA_1B_LAYER)
+        moved = layer_bytes + sum(2 * m * (n + k) for _, _, n, k in LLAMA_1B_LAYER)
+        stack[f"m{m}"] = {"us_per_layer": us_layer, "gbs": moved / us_layer / 1e3, "frac_of_measured_hbm": moved / us_layer / 1e3 / peak}
+    x = x_of(4, 8192, 4)
+    stack["rel_l2_sampled_rows_down_m4"] = sampled_parity(x, layers[0][6], kernels.fused_matmul(x, layers[0][6], out_dtype=torch.float32))
+    stack["layer_bytes"] = layer_bytes
+    stack["note"] = "16 distinct layers (621 MB) in one CUDA graph, seven fused launches per layer"
+    out["llama_1b_layer_q4_k_m"] = stack
+    del layers
+    torch.cuda.empty_cache()
+
+    # ---- Llama-3-8B shapes in Q5_K / Q6_K through the public matmul at 1, 32, 128, 512 tokens (the router picks the route)
+    shapes = {}
+    for tag, q, n, k in LLAMA_8B_SHAPES:
+        qt = QT[q]
+        nbytes = wbytes(qt, n, k)
+        copies = max(3, -(-300_000_000 // nbytes))
+        ws = [synth.make_weight_on_device(n, k, qt, seed=70 + c, device=dev) for c in range(copies)]
+        cap = gj.fused_batch_limit(ws[0])
+        row = {"fused_batch_limit": cap}
+        for m in (1, 32, 128, 512):
+            x = x_of(m, k, m)
+            us = _graph_us([(lambda w=w: gj.matmul(x, w)) for w in ws * 2], repeats=3)
+            moved = nbytes + 2 * m * k + 2 * m * n
+            flops = 2.0 * m * n * k
+            row[f"m{m}"] = {"us": us, "route": "fused" if m <= cap else "decode kernel + library GEMM", "gbs": moved / us / 1e3,
+                            "tflops": flops / us / 1e6, "frac_of_measured_hbm": moved / us / 1e3 / peak,
+                            "frac_of_sustained_bf16": flops / us / 1e6 / tf_peak}
+        x = x_of(32, k, 32)
+        row["rel_l2_sampled_rows_m32"] = sampled_parity(x, ws[0], gj.matmul(x, ws[0]))     # bf16 output: ~1.6e-3 is its rounding
+        shapes[f"{tag}_{q}_{n}x{k}"] = row
+        del ws
+        torch.cuda.empty_cache()
+    out["llama_8b_shapes"] = shapes
+
+    # ---- the decode kernel: bytes in + bytes out per second
+    dec = {}
+    for q in ("Q4_K", "Q6_K", "IQ4_XS", "IQ2_XS"):
+        qt = QT[q]
+        n, k = 16384, 8192
+        ws = [synth.make_weight_on_device(n, k, qt, seed=90 + c, device=dev) for c in range(3)]
+        for dt, item in ((torch.bfloat16, 2), (torch.float32, 4)):
+            us = _graph_us([(lambda w=w: w.dequantize(dt)) for w in ws * 2], repeats=3)
+            moved = wbytes(qt, n, k) + n * k * item
+            dec[f"{q}_{'bf16' if item == 2 else 'f32'}"] = {"us": us, "gbs": moved / us / 1e3, "frac_of_measured_hbm": moved / us / 1e3 / peak}
+        del ws
+        torch.cuda.empty_cache()
+    out["dequantize_16384x8192"] = dec
+    return out
+
+
 def check_headline(world, rank, dev, qt, weights, x, step, y_local, use_peer, y_full) -> dict:
     """Outside the timed region: run the timed step once more for each weight copy and compare what it
     left behind (the whole gathered output on every rank) with the CPU checker on sampled rows of this
@@ -630,6 +776,13 @@ def run_ours(args) -> None:
         except Exception as e:  # noqa: BLE001
             decode = {"unavailable": f"{type(e).__name__}: {e}"}
 
+    legs = None
+    if world == 1 and not args.no_legs:
+        try:
+            legs = extra_legs(dev)
+        except Exception as e:  # noqa: BLE001
+            legs = {"unavailable": f"{type(e).__name__}: {e}"}
+
     if rank == 0:
         cpu = cpu_baseline() if world == 1 else None
         line = {
@@ -664,6 +817,8 @@ def run_ours(args) -> None:
         }
         if decode is not None:
             line["decode"] = decode
+        if legs is not None:
+            line["legs"] = legs
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line))
@@ -688,6 +843,7 @@ def main() -> None:
     ap.add_argument("--profile-qtype", default=QTYPE_NAME, choices=["Q4_K", "Q5_K", "Q6_K"],
                     help="with --profile: the qtype of the 8192x28672 weight (each has its own tuned kernel)")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-step (tokens/s) leg")
+    ap.add_argument("--no-legs", action="store_true", help="skip the one-GPU legs for the other configurations")
     ap.add_argument("--profile", action="store_true",
                     help="profiler-friendly run: a few eager launches of the hot kernel, no graph, "
                          "no CPU baseline, no end-to-end leg, no JSON line")

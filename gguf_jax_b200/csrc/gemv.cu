@@ -90,8 +90,13 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
     else if (qtype == QT_Q6_K && gemv_q6k_applicable(N, K, 1, w, x_bf16)) tuned = gemv_q6k;
   }
   static const bool m1_tiled = [] { const char* e = getenv("GGQ_Q4K_M1_TILED"); return e && e[0] == '1'; }();
-  const bool dedicated_m1 = qtype == QT_Q4_K || qtype == QT_Q5_K || qtype == QT_Q6_K;   // these keep their batch-1 kernels
-  const bool tile_first = !dedicated_m1 || M > 1 || m1_tiled;
+  // Q4_K / Q5_K / Q6_K keep their batch-1 kernels, and from five batch rows on their integer-code MMA kernel
+  // (gemv_mma.cu) is as fast or faster than the tiled kernel (measured on B200: Q4_K 8192 x 28672 at batch 8
+  // 100 us either way, at batch 16 153 us against 2 x 101 us; on a 9 MB weight 10 us against 19 us at batch 8).
+  // The tiled kernel takes their batches 2..4 (Q4_K 8192 x 28672: 36 / 49 us at batch 2 / 4, against 64 / 98 us)
+  // and every batch of the formats that have nothing better.
+  const bool k_quant = qtype == QT_Q4_K || qtype == QT_Q5_K || qtype == QT_Q6_K;
+  const bool tile_first = !k_quant || (M >= 2 && M <= 4) || (M == 1 && m1_tiled);
   const int tile_max = gemv_tile_max_batch(qtype);
   const int tile_m = M < tile_max ? M : tile_max;
   const size_t tile_need = tile_max ? gemv_tile_workspace_bytes(qtype, N, K, tile_m) : 0;

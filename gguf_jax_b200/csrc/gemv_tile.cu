@@ -268,8 +268,10 @@ gemv_tile_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat1
     const uint32_t e = pp.flags[pp.rank][pp.world];
     out_tag = peer_tag_of(e + 1) << 16;
     x_tag = peer_tag_of(e + 1 - (uint32_t)pp.x_back) << 16;
-    if (pp.after_tagged && warp == 0)
-      peer_wait_tagged(pp.after_tagged, pp.after_words, peer_tag_of(e + 1 - (uint32_t)pp.after_back) << 16, lane, 32, status);
+    // every thread polls its own few words: the wait is a chain of L2 round trips, so it is the number of
+    // words per thread, not the number of threads, that costs time
+    if (pp.after_tagged)
+      peer_wait_tagged(pp.after_tagged, pp.after_words, peer_tag_of(e + 1 - (uint32_t)pp.after_back) << 16, tid, kThreads, status);
   }
   __syncthreads();
 
