@@ -47,6 +47,10 @@ extern "C" size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32
     if (cudaGetDevice(&dev) != cudaSuccess) { dev = -1; (void)cudaGetLastError(); }
     const size_t g = gemm_workspace_bytes(N, K, M, sm_count_of(dev));
     if (g > need) need = g;
+    if (gemm_codes_applicable(qtype, N, K, M)) {
+      const size_t c = gemm_codes_workspace_bytes(qtype, N, K, M, sm_count_of(dev));
+      if (c > need) need = c;
+    }
   }
   return need;
 }
@@ -261,8 +265,15 @@ extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, 
   const uint8_t* tab = device_tables(dev);
   if (ti->needs_tables && !tab)
     return fail(GGQ_NO_TABLES, "ggq_gemm: call ggq_set_tables(%d, ...) before using qtype %d", dev, qtype);
-  cudaError_t err = gemm_tf32(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, device_status_word(dev),
-                              workspace, workspace_bytes, sm_count_of(dev), (cudaStream_t)stream);
+  cudaError_t err;
+  static const bool tf32_only = [] { const char* e = getenv("GGQ_GEMM_TF32"); return e && e[0] == '1'; }();
+  if (!tf32_only && gemm_codes_applicable(qtype, N, K, M) && workspace && (uintptr_t)workspace % 256 == 0 &&
+      workspace_bytes >= gemm_codes_workspace_bytes(qtype, N, K, M, sm_count_of(dev)))
+    err = gemm_codes(qtype, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, device_status_word(dev), workspace, workspace_bytes,
+                     sm_count_of(dev), (cudaStream_t)stream);
+  else
+    err = gemm_tf32(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, device_status_word(dev), workspace, workspace_bytes,
+                    sm_count_of(dev), (cudaStream_t)stream);
   if (err != cudaSuccess) return fail(GGQ_LAUNCH_FAILED, "ggq_gemm: %s", cudaGetErrorString(err));
   return GGQ_OK;
 }

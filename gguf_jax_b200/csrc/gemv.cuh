@@ -250,6 +250,13 @@ cudaError_t gemm_tf32(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K
                       int y_dtype, const uint8_t* tab, int* status, void* ws, size_t ws_bytes, int sm_count,
                       cudaStream_t st);
 
+// Medium batches of Q4_K / Q5_K / Q6_K: tcgen05 kernel with exact integer codes as bf16 operands and one
+// TMEM slot per scale group (gemm_codes.cu).
+bool gemm_codes_applicable(int qtype, int64_t N, int64_t K, int M);
+size_t gemm_codes_workspace_bytes(int qtype, int64_t N, int64_t K, int M, int sm_count);
+cudaError_t gemm_codes(int qtype, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y, int y_dtype,
+                       int* status, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st);
+
 // Fixed offsets inside the caller's scratch: GEMV partial slots first, then the arrival counters
 // of every kernel (each launch leaves them at zero), then the float32 partial tiles of the GEMM.
 constexpr size_t kWsCounterOffset = (size_t)256 * 2 * 64 * sizeof(float);   // 128 KB
