@@ -50,7 +50,7 @@ constexpr int kSlots = 4;            // TMEM slots (scale groups) per buffer
 constexpr int kTmemCols = 2 * kSlots * kMT;     // 512
 constexpr int kMaxSplits = 8;
 constexpr int kSmemLimit = 232448;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 18;        // tries of up to 2 us each
 
 constexpr int kABytes = kTileN * kPhaseK * 2;    // 32 KB: two atoms of 128 rows x 128 B
 constexpr int kBBytes = kMT * kPhaseK * 2;       // 16 KB: two atoms of 64 rows x 128 B
@@ -69,9 +69,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"      // may sleep up to %3 ns: a waiting warp
+      "selp.u32 %0, 1, 0, p;\n\t}"                                          // must not take issue slots from the others
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(2000u) : "memory");
   return ok != 0;
 }
 // Bounded wait; returns false (and raises the flags) when it gives up.
@@ -122,6 +122,17 @@ __device__ __forceinline__ float pow2f(int e) { return __uint_as_float((uint32_t
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&p);
+}
+
+// Packed float32 pairs (Blackwell executes fma.rn.f32x2 as one instruction).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  return (uint64_t)__float_as_uint(lo) | ((uint64_t)__float_as_uint(hi) << 32);
+}
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) { return (uint64_t)lo | ((uint64_t)hi << 32); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
 }
 
 // The fold of a format as two coefficients: contribution = a * acc + b * sum(x).
@@ -299,6 +310,23 @@ gemm_codes_kernel(const uint8_t* __restrict__ w, int N, int K, const uint4* __re
     tf::Tables tb{};
     bool alive = true;
     int ph = 0;
+    constexpr int kBx = kMT * (kPhaseK / 8) / kProducers;             // 16-byte groups of the B tile per thread: 4
+    uint4 bx[kBx];
+    float xsum = 0.f;
+    auto fetch_b = [&](int blk, int pb) {
+#pragma unroll
+      for (int u = 0; u < kBx; u++) {
+        const int q = ptid + u * kProducers;
+        const int mr = q >> 4, ch = q & 15;                         // batch row of the tile, 16-byte chunk of the phase
+        bx[u] = make_uint4(0, 0, 0, 0);
+        if (m0 + mr < M)
+          bx[u] = __ldg(xp + (int64_t)(m0 + mr) * n_oct_row + (int64_t)blk * (4 * F::kOct) + pb * (kPhaseK / 8) + ch);
+      }
+      const int g = ptid / kMT, mr = ptid % kMT;                   // 4 x 64 sums per phase
+      xsum = 0.f;
+      if (g < Sh::kGroupsPerPhase && m0 + mr < M)
+        xsum = __ldg(xs + ((int64_t)(m0 + mr) * SB + blk) * (4 * Sh::kGroupsPerRun) + pb * Sh::kGroupsPerPhase + g);
+    };
     for (int b = 0; b < n_blocks; b++) {
       // every producer thread passes every one of these barriers, also after a wait has given up
       asm volatile("cp.async.wait_group 1;" ::: "memory");             // my pieces of block b have landed
@@ -312,22 +340,9 @@ gemm_codes_kernel(const uint8_t* __restrict__ w, int N, int K, const uint4* __re
         const int s = ph & 1, it = ph >> 1;
         if (it > 0 && !mbar_wait(empty_bar(s), (it - 1) & 1, abort_flag, status)) { alive = false; break; }
         const uint32_t stage = smem_base + s * kStageBytes;
-        // ---- B tile: 64 batch rows x 16 groups of eight activations, and the groups' sums
-        uint4 bx[kMT * (kPhaseK / 8) / kProducers];
-#pragma unroll
-        for (int u = 0; u < kMT * (kPhaseK / 8) / kProducers; u++) {
-          const int q = ptid + u * kProducers;
-          const int mr = q >> 4, ch = q & 15;                       // batch row of the tile, 16-byte chunk of the phase
-          bx[u] = make_uint4(0, 0, 0, 0);
-          if (m0 + mr < M)
-            bx[u] = __ldg(xp + (int64_t)(m0 + mr) * n_oct_row + (int64_t)blk * (4 * F::kOct) + pb * (kPhaseK / 8) + ch);
-        }
-        float xsum = 0.f;
-        {
-          const int g = ptid / kMT, mr = ptid % kMT;               // 4 x 64 sums per phase
-          if (g < Sh::kGroupsPerPhase && m0 + mr < M)
-            xsum = __ldg(xs + ((int64_t)(m0 + mr) * SB + blk) * (4 * Sh::kGroupsPerRun) + pb * Sh::kGroupsPerPhase + g);
-        }
+        // ---- B tile (64 batch rows x 16 groups of eight activations) and the groups' sums: fetched one phase
+        // ahead (the L2 round trip overlaps the wait above and the code extraction below)
+        if (ph == 0) fetch_b(blk, pb);
         // ---- A tile: this thread's octets of (row, run)
         const int run = pb * Sh::kRunsPerPhase + t_run;
         const typename F::Run rr = F::load_run(ld, run);
@@ -349,7 +364,7 @@ gemm_codes_kernel(const uint8_t* __restrict__ w, int N, int K, const uint4* __re
           }
         }
 #pragma unroll
-        for (int u = 0; u < kMT * (kPhaseK / 8) / kProducers; u++) {
+        for (int u = 0; u < kBx; u++) {
           const int q = ptid + u * kProducers;
           const int mr = q >> 4, ch = q & 15;
           sts_v4(stage + kABytes + (ch >> 3) * (kMT * 128) + swz(mr, ch & 7), bx[u].x, bx[u].y, bx[u].z, bx[u].w);
@@ -359,6 +374,9 @@ gemm_codes_kernel(const uint8_t* __restrict__ w, int N, int K, const uint4* __re
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(full_bar(s));
+        // the next phase's activations (of this block, or of the first phase of the next one)
+        if (pb + 1 < Sh::kPhasesPerBlock) fetch_b(blk, pb + 1);
+        else if (b + 1 < n_blocks) fetch_b(blk + 1, 0);
       }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -368,9 +386,9 @@ gemm_codes_kernel(const uint8_t* __restrict__ w, int N, int K, const uint4* __re
     const int e = warp - kProducerWarps;
     const int quarter = e & 3, chalf = e >> 2;
     const int row = 32 * quarter + lane;
-    float out[32];
+    uint64_t out2[16];             // 32 running outputs as 16 float pairs
 #pragma unroll
-    for (int i = 0; i < 32; i++) out[i] = 0.f;
+    for (int i = 0; i < 16; i++) out2[i] = 0ull;
     bool ok = true;
     for (int ph = 0; ph < n_phases && ok; ph++) {
       const int s = ph & 1, it = ph >> 1;
@@ -393,13 +411,13 @@ gemm_codes_kernel(const uint8_t* __restrict__ w, int N, int K, const uint4* __re
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const float2 ab = *reinterpret_cast<const float2*>(stage + kABytes + kBBytes + (g * kTileN + row) * 8);
         const float4* sx = reinterpret_cast<const float4*>(stage + kABytes + kBBytes + kScBytes + (g * kMT + 32 * chalf) * 4);
+        // two batch columns per instruction (fma.rn.f32x2): out = a * D + (b * sum(x) + out)
+        const uint64_t a2 = pack2(ab.x, ab.x), b2 = pack2(ab.y, ab.y);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           const float4 s4 = sx[i];
-          out[4 * i + 0] = fmaf(ab.x, __uint_as_float(v[4 * i + 0]), fmaf(ab.y, s4.x, out[4 * i + 0]));
-          out[4 * i + 1] = fmaf(ab.x, __uint_as_float(v[4 * i + 1]), fmaf(ab.y, s4.y, out[4 * i + 1]));
-          out[4 * i + 2] = fmaf(ab.x, __uint_as_float(v[4 * i + 2]), fmaf(ab.y, s4.z, out[4 * i + 2]));
-          out[4 * i + 3] = fmaf(ab.x, __uint_as_float(v[4 * i + 3]), fmaf(ab.y, s4.w, out[4 * i + 3]));
+          out2[2 * i] = fma2(a2, pack2u(v[4 * i], v[4 * i + 1]), fma2(b2, pack2(s4.x, s4.y), out2[2 * i]));
+          out2[2 * i + 1] = fma2(a2, pack2u(v[4 * i + 2], v[4 * i + 3]), fma2(b2, pack2(s4.z, s4.w), out2[2 * i + 1]));
         }
       }
       // the slots and the stage's scales are consumed
@@ -414,7 +432,7 @@ gemm_codes_kernel(const uint8_t* __restrict__ w, int N, int K, const uint4* __re
       for (int i = 0; i < 32; i++) {
         const int m = m0 + 32 * chalf + i;
         if (m < M) {
-          const float val = out[i] * pow2f(133 - __ldg(S_in + m));
+          const float val = __uint_as_float((uint32_t)(out2[i >> 1] >> (32 * (i & 1)))) * pow2f(133 - __ldg(S_in + m));
           if (splits == 1) store_out(y, y_dtype, (int64_t)m * N + out_row, val);
           else partials[((int64_t)split * M + m) * N + out_row] = val;
         }
