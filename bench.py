@@ -183,15 +183,18 @@ def _scale_block_scales(w, log2: int) -> None:
     blocks[:, cols] = (f.float() * (2.0 ** log2)).to(torch.float16).view(torch.uint8)
 
 
-def decode_leg(world: int, rank: int, dev) -> dict:
-    """Time one decode step (batch 1) of the 70B-shaped model; see the module docstring.
+def decode_leg(world: int, rank: int, dev, batch: int = 1, route: str = "fused") -> dict:
+    """Time one decode step of the 70B-shaped model at `batch` sequences; see the module docstring.
 
     The GEMVs are chained for real: q+k and v read the previous layer's down output, o reads the
     first 8192 outputs of q+k, gate+up reads o, down reads the first 28672 outputs of gate+up, the
     lm_head reads the last down output.  (Attention, norms and activations are not run, so the
     numbers mean nothing; the block scales are shifted by powers of two beforehand so that the
     magnitudes stay near one along the chain.)  On N > 1 ranks every product is row-sharded and
-    its result reaches every rank through the tagged exchange inside the kernels."""
+    its result reaches every rank through the tagged exchange inside the kernels (batch 1) or an
+    NCCL all-gather after the kernel (larger batches: the in-kernel exchanges are batch-1 paths).
+    `route` "fused" calls the fused kernels by name (above the small-batch cap that is the tcgen05
+    code GEMM); "router" calls `matmul`, which above the cap decodes and calls the library GEMM."""
     import torch
     import torch.distributed as dist
     from gguf.constants import GGMLQuantizationType as QT
@@ -214,9 +217,17 @@ def decode_leg(world: int, rank: int, dev) -> dict:
               for li in range(DECODE_DISTINCT)]
     head = shard(DECODE_HEAD[1], DECODE_HEAD[2], DECODE_HEAD[3], 999)
     launches = DECODE_LAYERS * len(DECODE_LAYER) + 1
-    x0 = torch.from_numpy(synth.make_x(1, 8192, seed=8192)).to(dev).to(torch.bfloat16)
+    x0 = torch.from_numpy(synth.make_x(batch, 8192, seed=8192)).to(dev).to(torch.bfloat16)
+    product = kernels.fused_matmul if route == "fused" else gj.matmul
 
-    if world > 1:
+    if batch > 1:
+        def mm(x, w):
+            return sharded.gather_columns(product(x[:, :w.shape[1]].contiguous(), w)) if world > 1 else \
+                product(x[:, :w.shape[1]].contiguous(), w)
+
+        def value(h):
+            return h
+    elif world > 1:
         ex = sharded.TaggedExchange(None, n_max=DECODE_HEAD[2], device=dev,
                                     n_buffers=sharded.TaggedExchange.buffers_for(launches, max_back=2))
 
@@ -319,19 +330,41 @@ def decode_leg(world: int, rank: int, dev) -> dict:
         ms = float(t.item())
     lv = value(logits).float()
     finite = bool(torch.isfinite(lv).all())
-    # parity of the last product of the chain: sampled rows of this rank's lm_head shard against the
-    # CPU checker fed with the hidden vector the chain produced; and a checksum of the logits, which
-    # must agree between runs at N = 1, 2, 4, 8 (same weights, same calibration) up to the last-place
-    # differences of a different split order
+    # parity along the chain: every product of the first layer step and the lm_head, each fed with the
+    # vector the chain itself produced, on sampled rows of this rank's shard against the CPU checker.
+    # The logits themselves are NOT comparable between N to the last place: the chain is linear and
+    # unnormalised (80 products of non-normal random matrices), so the last-place differences of a
+    # different split order grow to per cents of a common scale factor by the end; the checksum is
+    # there to show that, not to be matched.
     import numpy as np
     from oracle import oracle as O
-    hv = value(last_hidden[0]).float().reshape(1, -1)[:, :DECODE_HEAD[3]]
-    rows_local = DECODE_HEAD[2] // world
-    pick = np.sort(np.random.default_rng(7).choice(rows_local, size=64, replace=False))
-    w_rows = head.data[torch.from_numpy(pick).to(dev)].cpu().numpy()
-    ref = O.c_matmul(O.bf16_bits(hv.cpu().numpy()), w_rows, QT[DECODE_HEAD[1]]).reshape(-1)
-    got = lv.reshape(-1)[rank * rows_local + torch.from_numpy(pick).to(dev)].cpu().numpy()
-    head_err = torch.tensor([O.rel_l2(got, ref)], device=dev, dtype=torch.float64)
+
+    def product_error(x_full, w, y_full, n_pick, seed):
+        rows_local = w.shape[0]
+        pick = np.sort(np.random.default_rng(seed).choice(rows_local, size=min(n_pick, rows_local), replace=False))
+        w_rows = w.data[torch.from_numpy(pick).to(dev)].cpu().numpy()
+        xin = x_full.float().reshape(batch, -1)[:, :w.shape[1]].cpu().numpy()
+        ref = O.c_matmul(O.bf16_bits(xin), w_rows, w.qtype)
+        got = y_full.float().reshape(batch, -1)[:, rank * rows_local + torch.from_numpy(pick).to(dev)].cpu().numpy()
+        return O.rel_l2(got, ref)
+
+    errs = [product_error(value(last_hidden[0]), head, lv, 64, 7)]
+    ws0 = layers[0]
+    h0 = x0
+    qk = value(mm(x0, ws0[0]))
+    errs.append(product_error(h0, ws0[0], qk, 32, 11))
+    vv = value(mm(x0, ws0[1]))
+    errs.append(product_error(h0, ws0[1], vv, 32, 12))
+    qk_h = mm(x0, ws0[0])
+    o_h = mm(qk_h, ws0[2])
+    o_v = value(o_h)
+    gu_h = mm(o_h, ws0[3])
+    gu_v = value(gu_h)
+    d_v = value(mm(gu_h, ws0[4]))
+    errs.append(product_error(qk, ws0[2], o_v, 32, 13))
+    errs.append(product_error(o_v, ws0[3], gu_v, 32, 14))
+    errs.append(product_error(gu_v, ws0[4], d_v, 32, 15))
+    head_err = torch.tensor([errs[0], max(errs)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(head_err, op=dist.ReduceOp.MAX)
     checksum = {"logits_abs_mean": float(lv.abs().mean()), "logits_sum": float(lv.double().sum()),
@@ -339,12 +372,18 @@ def decode_leg(world: int, rank: int, dev) -> dict:
     wbytes = sum(n * (k // 256) * _BLOCK_BYTES[q] for _, q, n, k in DECODE_LAYER) * DECODE_LAYERS
     wbytes += DECODE_HEAD[2] * (DECODE_HEAD[3] // 256) * _BLOCK_BYTES[DECODE_HEAD[1]]
     del graph
-    return {"tok_s": 1e3 / ms, "ms_per_token": ms, "batch": 1, "launches_per_token": launches,
-            "weight_gb_per_token": wbytes / 1e9, "aggregate_hbm_gbs": wbytes / (ms * 1e-3) / 1e9,
+    exchange = "none" if world == 1 else (
+        "NCCL all-gather after each kernel" if batch > 1 else
+        "tagged words stored into every rank's buffer by the kernels (ggq_gemv_sharded_tagged)")
+    return {"tok_s": batch * 1e3 / ms, "ms_per_token": ms / batch, "ms_per_step": ms, "batch": batch, "route": route, "launches_per_step": launches,
+            "weight_gb_per_step": wbytes / 1e9, "aggregate_hbm_gbs": wbytes / (ms * 1e-3) / 1e9,
             "logits_finite": finite, "logits_rms": float(lv.pow(2).mean().sqrt()), "device_status": device_status(),
-            "parity": {"lm_head_rel_l2_vs_oracle": float(head_err.item()), "rows": 64 * world, "bar": 2e-3},
+            "parity": {"lm_head_rel_l2_vs_oracle": float(head_err[0].item()),
+                       "worst_of_first_layer_and_head_rel_l2_vs_oracle": float(head_err[1].item()),
+                       "rows": (64 + 5 * 32) * world, "bar": 2e-3,
+                       "note": "each product fed with the vector the chain produced; sampled rows of every rank's shard"},
             "checksum": checksum,
-            "exchange": "tagged words stored into every rank's buffer by the kernels (ggq_gemv_sharded_tagged)" if world > 1 else "none",
+            "exchange": exchange,
             "model": "Llama-3-70B-shaped Q4_K_M (attn_v, ffn_down, lm_head in Q6_K), GEMVs only, chained",
             "note": f"{DECODE_LAYERS} layer steps cycle over {DECODE_DISTINCT} distinct synthetic layer weight sets "
                     "(each far larger than L2); block scales shifted by powers of two so the chain stays near unit "
@@ -589,6 +628,18 @@ def run_ours(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     _lib.lib()
+    if args.profile and (args.profile_shape or args.profile_batch != BATCH or args.profile_qtype not in ("Q4_K", "Q5_K", "Q6_K")):
+        # any format, shape and batch through the public product: three distinct weights in turn
+        n_rows, k_dim = (int(v) for v in (args.profile_shape or f"{N_ROWS}x{K_DIM}").lower().split("x"))
+        qt = QT[args.profile_qtype]
+        ws = [synth.make_weight_on_device(n_rows, k_dim, qt, seed=c, device=dev) for c in range(3)]
+        xp = torch.from_numpy(synth.make_x(args.profile_batch, k_dim, seed=0)).to(dev).to(torch.bfloat16)
+        for i in range(args.warmup + args.steps):
+            kernels.fused_matmul(xp, ws[i % 3])
+        torch.cuda.synchronize()
+        print(f"profile run: {args.warmup + args.steps} eager launches of {qt.name} {n_rows}x{k_dim} batch "
+              f"{args.profile_batch} done", file=sys.stderr)
+        return
     qt = QT[args.profile_qtype if args.profile else QTYPE_NAME]
 
     rows_local = N_ROWS // world
@@ -736,12 +787,9 @@ def run_ours(args) -> None:
 
     def e2e_step(i: int):
         xd = xh.to(dev, non_blocking=True)
-        if use_peer[0]:
-            y = peer.matmul(xd.reshape(-1), weights[i % copies])
-            torch.cuda.current_stream().synchronize()
-            dist.barrier()              # every rank's rows have landed before the host reads them
-            yh.copy_(y.to_tensor(), non_blocking=True)
-        elif world > 1:
+        if world > 1:
+            # the public sharded call: local fused product, then the all-gather, all stream-ordered (the
+            # in-kernel exchange orders launches against each other, not against a host read-back)
             y = gj.matmul(xd, weights[i % copies])
             dist.all_gather_into_tensor(y_full, y)
             yh.view(world, BATCH, rows_local).copy_(y_full, non_blocking=True)
@@ -775,6 +823,17 @@ def run_ours(args) -> None:
             decode = decode_leg(world, rank, dev)
         except Exception as e:  # noqa: BLE001
             decode = {"unavailable": f"{type(e).__name__}: {e}"}
+        torch.cuda.empty_cache()
+        # the same step at 32 sequences: above the small-batch cap, so the fused route is the tcgen05
+        # code GEMM called by name; on one GPU the router's route (decode + library GEMM) is timed beside it
+        try:
+            decode["batch32"] = decode_leg(world, rank, dev, batch=32, route="fused")
+            torch.cuda.empty_cache()
+            if world == 1:
+                decode["batch32_router"] = decode_leg(world, rank, dev, batch=32, route="router")
+                torch.cuda.empty_cache()
+        except Exception as e:  # noqa: BLE001
+            decode["batch32"] = {"unavailable": f"{type(e).__name__}: {e}"}
 
     legs = None
     if world == 1 and not args.no_legs:
@@ -804,7 +863,9 @@ def run_ours(args) -> None:
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "peak_source": peak_src,
                 "traffic": (NCU_TRAFFIC_BYTES_PER_LAUNCH * rows_local // N_ROWS) if NCU_TRAFFIC_BYTES_PER_LAUNCH else None,
-                "traffic_source": NCU_TRAFFIC_SOURCE,
+                "traffic_source": NCU_TRAFFIC_SOURCE + ("" if world == 1 else
+                                                         "; scaled by rows_per_gpu / 8192, not captured on a shard (every weight "
+                                                         "row is read once, so traffic grows in proportion to the rows)"),
                 "algorithmic_bytes_per_launch": launch_bytes, "launch_us": launch_ms * 1e3,
             },
             "clocks": clk,
@@ -840,8 +901,12 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-qtype", default=QTYPE_NAME, choices=["Q4_K", "Q5_K", "Q6_K"],
-                    help="with --profile: the qtype of the 8192x28672 weight (each has its own tuned kernel)")
+    ap.add_argument("--profile-qtype", default=QTYPE_NAME,
+                    choices=["Q4_K", "Q5_K", "Q6_K", "Q2_K", "IQ4_XS", "IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S",
+                             "IQ1_S", "IQ1_M"],
+                    help="with --profile: the qtype of the weight")
+    ap.add_argument("--profile-shape", default="", help="with --profile: ROWSxCOLS of the weight (default 8192x28672)")
+    ap.add_argument("--profile-batch", type=int, default=BATCH, help="with --profile: rows of x (default 1)")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-step (tokens/s) leg")
     ap.add_argument("--no-legs", action="store_true", help="skip the one-GPU legs for the other configurations")
     ap.add_argument("--profile", action="store_true",

@@ -720,7 +720,6 @@ cudaError_t gemv_tile(int qtype, const uint8_t* w, int64_t N, int64_t K, const v
   case QT: return launch_passes<tf::F>(MP, geo, grid, st, w, (int)N, (int)K, x, M, y, y_dtype, counters, slots, pp, status, tab);
   switch (qtype) {
     GGQ_TILE_CASE(QT_Q4_K, Q4K)
-#ifndef GGQ_TILE_FEW_FORMATS
     GGQ_TILE_CASE(QT_Q5_K, Q5K)
     GGQ_TILE_CASE(QT_Q6_K, Q6K)
     GGQ_TILE_CASE(QT_Q2_K, Q2K)
@@ -731,7 +730,6 @@ cudaError_t gemv_tile(int qtype, const uint8_t* w, int64_t N, int64_t K, const v
     GGQ_TILE_CASE(QT_IQ3_S, IQ3S)
     GGQ_TILE_CASE(QT_IQ1_S, IQ1S)
     GGQ_TILE_CASE(QT_IQ1_M, IQ1M)
-#endif
     GGQ_TILE_CASE(QT_IQ2_XXS, IQ2XXS)
     default: return cudaErrorInvalidValue;
   }

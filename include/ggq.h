@@ -93,10 +93,12 @@ int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K);
 /* Largest M served by the small-batch (GEMV) kernel; above it ggq_gemm is used. */
 int32_t ggq_gemv_max_batch(void);
 
-/* Scratch the fused kernels need for an (N, K) weight at batch M.  The caller
- * allocates at least this many bytes, 256-byte aligned, ZERO-FILLED ONCE; the kernels
- * leave it zeroed again, so one buffer serves any number of calls that do not overlap
- * on the GPU. */
+/* Scratch the fused kernels need for an (N, K) weight at batch M: the largest need of any kernel
+ * ggq_gemv / ggq_gemm may pick for that shape (split-K partials, per-row-tile step counters,
+ * per-unit partial slots).  The caller allocates at least this many bytes, 256-byte aligned,
+ * ZERO-FILLED ONCE; the kernels leave it zeroed again, so one buffer serves any number of calls
+ * that do not overlap on the GPU.  With less scratch than this the launchers fall back to the
+ * kernels that need none where there is one, and return GGQ_INVALID_VALUE otherwise. */
 size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32_t M);
 
 /* y[M, N] = x[M, K] @ W[N, K]^T with W quantized (row-major blocks, N rows of
@@ -106,20 +108,32 @@ size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32_t M);
  * Replaces matmul_q4_k / matmul_q5_k / matmul_q6_k / matmul_iq4_xs / matmul_lowbit
  * (src/gguf_jax/cute/q4_k.py:282-329, q5_k.py:150-179, q6_k.py:115-144,
  * iq4_xs.py:146-175, lowbit.py:675-712).
- * The batch-1 kernels for Q4_K, Q5_K and Q6_K are launched as programmatic dependents: they may
- * begin to read `w` (only `w`) while the previous launch of this library on the same stream is
- * still finishing.  So `w` must not be an output of that previous launch; x, y and the
- * workspace carry no such restriction.  The weight buffer must extend to the next 16-byte
- * boundary (true of any device allocation). */
+ * Which kernel runs (all give the same product to float32 rounding; none is a CPU path):
+ *   Q4_K / Q5_K / Q6_K at M = 1 and M = 5..16: the per-format kernels (integer codes fed to
+ *     mma.sync as exact bf16 values, scales applied to the float32 accumulators);
+ *   Q4_K / Q5_K / Q6_K at M = 2..4, and Q2_K, IQ4_XS, IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S,
+ *     IQ1_S, IQ1_M at every M: the tiled kernel (same arithmetic; warps own contiguous ranges of
+ *     16-row x K-chunk steps; needs K % 256 == 0, rows of a multiple of 16 bytes and the workspace; serves M in slices of 8);
+ *   everything else (the 32-element formats, float formats, shapes the above do not take): the
+ *     streaming kernels that decode a block in registers and multiply it at once.
+ * Launches are programmatic dependents: a kernel may begin to read `w` (only `w`) while the
+ * previous launch of this library on the same stream is still finishing.  So `w` must not be an
+ * output of that previous launch; x, y and the workspace carry no such restriction.  The weight
+ * buffer must extend to the next 16-byte boundary (true of any device allocation). */
 int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
                  int32_t M, void* y, int32_t y_dtype, void* workspace,
                  size_t workspace_bytes, void* stream);
 
-/* Same product for larger M on the tcgen05 tensor-core path (any block qtype, K a multiple of
- * 32).  Replaces gemm_q4_k (src/gguf_jax/cute/q4_k_gemm.py:369-391).  With few row tiles the
- * launch cuts K into ranges and needs ggq_workspace_bytes(qtype, N, K, M) of scratch; without
- * it (NULL / too small) it runs one range per tile.  ggq_fused_batch_limit does not count this
- * kernel while it is slower than decode + library GEMM: callers pick it by name. */
+/* Same product for larger M on the tcgen05 tensor-core path.  Replaces gemm_q4_k
+ * (src/gguf_jax/cute/q4_k_gemm.py:369-391).  Two kernels:
+ *   Q4_K / Q5_K / Q6_K with K % 256 == 0 and the workspace: integer-code operands (exact in bf16),
+ *     one tensor-memory accumulator per scale group, float32 scales applied after the MMA -- no
+ *     rounding of the weight; x is used at its bf16 value; agrees with float32 arithmetic to 2e-5;
+ *   any other block qtype (K % 256 == 0), or the above without workspace: blocks decoded to
+ *     float32 and multiplied as tf32 (weights rounded to 10 mantissa bits; relative error 1e-3).
+ * With few row tiles a launch cuts K into ranges (partials in the workspace, last arriver adds
+ * them in a fixed order: results do not depend on timing).  ggq_fused_batch_limit does not count
+ * these kernels while they are slower than decode + library GEMM: callers pick ggq_gemm by name. */
 int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
                  int32_t M, void* y, int32_t y_dtype, void* workspace,
                  size_t workspace_bytes, void* stream);
