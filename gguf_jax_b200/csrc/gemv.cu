@@ -42,6 +42,10 @@ extern "C" size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32
     const size_t tile = tmax ? gemv_tile_workspace_bytes(qtype, N, K, M < tmax ? M : tmax) : 0;
     if (tile > need && K % 256 == 0) need = tile;
   }
+  if ((qtype == QT_Q4_K || qtype == QT_Q5_K || qtype == QT_Q6_K) && M >= 2 && K % 256 == 0) {
+    const size_t wd = gemv_wide_workspace_bytes(qtype, N, K, M, kMaxSmCount);
+    if (wd > need) need = wd;
+  }
   if (M > kGemvMaxBatch && gemm_applicable(ti, N, K, M)) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess) { dev = -1; (void)cudaGetLastError(); }
@@ -106,7 +110,13 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
   const size_t tile_need = tile_max ? gemv_tile_workspace_bytes(qtype, N, K, tile_m) : 0;
   const bool tile_ok = tile_first && tile_need && workspace && workspace_bytes >= tile_need && (uintptr_t)workspace % 256 == 0 &&
                        sm_count_of(dev) > 0 && gemv_tile_applicable(qtype, N, K, tile_m, w, x_bf16);
-  if (tile_ok) {
+  static const int wide_min = [] { const char* e = getenv("GGQ_WIDE_MIN"); return e ? atoi(e) : 5; }();
+  const bool wide_ok = k_quant && M >= wide_min && workspace && (uintptr_t)workspace % 256 == 0 && sm_count_of(dev) > 0 &&
+                       workspace_bytes >= gemv_wide_workspace_bytes(qtype, N, K, M, sm_count_of(dev)) &&
+                       gemv_wide_applicable(qtype, N, K, M, w, x_bf16);
+  if (wide_ok) {
+    err = gemv_wide(qtype, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev), st);
+  } else if (tile_ok) {
     // up to tile_max batch rows per launch; a larger batch reads the weight once per tile_max rows
     err = cudaSuccess;
     for (int m0 = 0; m0 < M && err == cudaSuccess; m0 += tile_max) {
@@ -267,7 +277,20 @@ extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, 
     return fail(GGQ_NO_TABLES, "ggq_gemm: call ggq_set_tables(%d, ...) before using qtype %d", dev, qtype);
   cudaError_t err;
   static const bool tf32_only = [] { const char* e = getenv("GGQ_GEMM_TF32"); return e && e[0] == '1'; }();
-  if (!tf32_only && gemm_codes_applicable(qtype, N, K, M) && workspace && (uintptr_t)workspace % 256 == 0 &&
+  static const int wide_max = [] { const char* e = getenv("GGQ_WIDE_GEMM_MAX"); return e ? atoi(e) : 128; }();
+  const int wide_slice = gemv_wide_max_batch();
+  const int y_item = y_dtype == GGQ_F32 ? 4 : 2;
+  if (!tf32_only && M <= wide_max && workspace && (uintptr_t)workspace % 256 == 0 &&
+      workspace_bytes >= gemv_wide_workspace_bytes(qtype, N, K, M < wide_slice ? M : wide_slice, sm_count_of(dev)) &&
+      gemv_wide_applicable(qtype, N, K, M < wide_slice ? M : wide_slice, w, x_bf16)) {
+    // slices of up to 32 batch rows through the exact-code mma.sync kernel: the weight is read once per slice
+    err = cudaSuccess;
+    for (int m0 = 0; m0 < M && err == cudaSuccess; m0 += wide_slice) {
+      const int mb = M - m0 < wide_slice ? M - m0 : wide_slice;
+      err = gemv_wide(qtype, (const uint8_t*)w, N, K, (const uint8_t*)x_bf16 + (size_t)m0 * K * 2, mb,
+                      (uint8_t*)y + (size_t)m0 * N * y_item, y_dtype, workspace, workspace_bytes, sm_count_of(dev), (cudaStream_t)stream);
+    }
+  } else if (!tf32_only && gemm_codes_applicable(qtype, N, K, M) && workspace && (uintptr_t)workspace % 256 == 0 &&
       workspace_bytes >= gemm_codes_workspace_bytes(qtype, N, K, M, sm_count_of(dev)))
     err = gemm_codes(qtype, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, device_status_word(dev), workspace, workspace_bytes,
                      sm_count_of(dev), (cudaStream_t)stream);

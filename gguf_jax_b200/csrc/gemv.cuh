@@ -250,6 +250,14 @@ cudaError_t gemm_tf32(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K
                       int y_dtype, const uint8_t* tab, int* status, void* ws, size_t ws_bytes, int sm_count,
                       cudaStream_t st);
 
+// Batches of 2 .. 32 rows per launch for Q4_K / Q5_K / Q6_K: all eight MMA columns are batch rows, one MMA
+// (pair) per scale group, float32 scales on the accumulators (gemv_wide.cu).  Needs the workspace.
+int gemv_wide_max_batch();
+bool gemv_wide_applicable(int qtype, int64_t N, int64_t K, int M, const void* w, const void* x);
+size_t gemv_wide_workspace_bytes(int qtype, int64_t N, int64_t K, int M, int sm_count);
+cudaError_t gemv_wide(int qtype, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y, int y_dtype,
+                      void* ws, size_t ws_bytes, int sm_count, cudaStream_t st);
+
 // Medium batches of Q4_K / Q5_K / Q6_K: tcgen05 kernel with exact integer codes as bf16 operands and one
 // TMEM slot per scale group (gemm_codes.cu).
 bool gemm_codes_applicable(int qtype, int64_t N, int64_t K, int M);
