@@ -9,17 +9,28 @@ namespace {
 constexpr int kGemvMaxBatch = 16;
 // From this batch on the tensor-core small-batch kernel beats the per-element FMA kernel.
 constexpr int kMmaMinBatch = 2;
-// Up to this batch the tuned batch-1 kernels are simply launched once per batch row.  Measured on
-// B200 the small-batch kernel costs 1.4 (12 MB weight) to 3 (130 MB) batch-1 launches for Q4_K and
-// Q5_K, and 3.3 (50 MB) to 4.8 (190 MB) for Q6_K.
+// Up to this batch the tuned batch-1 kernels are simply launched once per batch row (only where the
+// tiled kernel cannot run: no workspace, or rows that are not 16-byte aligned).
 inline int tuned_max_repeat(int qtype, int64_t weight_bytes) {
   if (qtype == QT_Q6_K) return weight_bytes < (24ll << 20) ? 2 : weight_bytes < (100ll << 20) ? 3 : 4;
   return weight_bytes < (24ll << 20) ? 1 : weight_bytes < (80ll << 20) ? 2 : 3;
 }
-// Measured on B200 the tcgen05 kernel behind ggq_gemm is still slower than the decode kernel
-// followed by a library bf16 GEMM (its producers wait on global loads), so
-// ggq_fused_batch_limit keeps the router at the small-batch cap and ggq_gemm is reached only
-// by name.
+inline bool is_k_quant(int qtype) { return qtype == QT_Q4_K || qtype == QT_Q5_K || qtype == QT_Q6_K; }
+// The batch-major kernel (gemv_wide.cu) costs two launches and a partial-sum settle, about 10 us on a weight
+// of a few MB, and then very little per batch row; the integer-code MMA kernel (gemv_mma.cu) starts at 4 us
+// and grows with the weight.  Measured crossover on B200 at 5..16 batch rows: about 20 MB for Q4_K / Q5_K
+// (8192 x 2048 and 4096 x 4096, 9 MB: 10-12 us against 14-18 us; 14336 x 4096, 33 MB: 28-35 us against 24-27 us),
+// about 10 MB for Q6_K (4096 x 4096, 14 MB: 20 us either way).
+inline bool wide_pays(int qtype, int64_t weight_bytes) {
+  return weight_bytes >= (qtype == QT_Q6_K ? (10ll << 20) : (20ll << 20));
+}
+// Above 16 batch rows the choice is between slices of 32 rows through the batch-major kernel and, in the
+// caller, the decode kernel followed by a library GEMM.  One slice wins from about 20 MB on (Q4_K 8192 x 8192:
+// 39 us against 76 us; Q6_K 14336 x 4096: 45 us against 66 us; Q5_K 4096 x 4096, 11.5 MB: 28 us against 23 us,
+// its decoded copy stays in the L2); two slices or more lose, so the router's cap is 32 there and 16 elsewhere.
+// The tcgen05 kernels behind ggq_gemm (integer-code and tf32 operands) are slower than both at every
+// batch measured and are reached only by name, above 128 rows or for the other formats.
+constexpr int kWideRouterBatch = 32;
 }
 
 extern "C" int32_t ggq_gemv_max_batch(void) { return kGemvMaxBatch; }
@@ -27,6 +38,9 @@ extern "C" int32_t ggq_gemv_max_batch(void) { return kGemvMaxBatch; }
 extern "C" int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K) {
   const TypeInfo* ti = type_info(qtype);
   if (!ti || !ti->fused || N <= 0 || K <= 0 || K % ti->block_elems) return 0;
+  if (is_k_quant(qtype) && K % 256 == 0 && (K / 256 * ti->block_bytes) % 16 == 0 &&
+      wide_pays(qtype, N * (K / 256) * (int64_t)ti->block_bytes) && gemv_wide_applicable(qtype, N, K, kWideRouterBatch, nullptr, nullptr))
+    return kWideRouterBatch;
   return kGemvMaxBatch;
 }
 
@@ -98,12 +112,11 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
     else if (qtype == QT_Q6_K && gemv_q6k_applicable(N, K, 1, w, x_bf16)) tuned = gemv_q6k;
   }
   static const bool m1_tiled = [] { const char* e = getenv("GGQ_Q4K_M1_TILED"); return e && e[0] == '1'; }();
-  // Q4_K / Q5_K / Q6_K keep their batch-1 kernels, and from five batch rows on their integer-code MMA kernel
-  // (gemv_mma.cu) is as fast or faster than the tiled kernel (measured on B200: Q4_K 8192 x 28672 at batch 8
-  // 100 us either way, at batch 16 153 us against 2 x 101 us; on a 9 MB weight 10 us against 19 us at batch 8).
-  // The tiled kernel takes their batches 2..4 (Q4_K 8192 x 28672: 36 / 49 us at batch 2 / 4, against 64 / 98 us)
-  // and every batch of the formats that have nothing better.
-  const bool k_quant = qtype == QT_Q4_K || qtype == QT_Q5_K || qtype == QT_Q6_K;
+  // Q4_K / Q5_K / Q6_K keep their batch-1 kernels; the tiled kernel takes their batches 2..4 (Q4_K 8192 x 28672:
+  // 36 / 49 us at batch 2 / 4) and every batch of the formats that have nothing better; from five batch rows on
+  // the batch-major kernel takes the larger weights (Q4_K 8192 x 28672: 68 / 77 us at batch 8 / 16 against
+  // 100 / 153 us) and the integer-code MMA kernel (gemv_mma.cu) the smaller ones (see wide_pays).
+  const bool k_quant = is_k_quant(qtype);
   const bool tile_first = !k_quant || (M >= 2 && M <= 4) || (M == 1 && m1_tiled);
   const int tile_max = gemv_tile_max_batch(qtype);
   const int tile_m = M < tile_max ? M : tile_max;
@@ -111,7 +124,7 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
   const bool tile_ok = tile_first && tile_need && workspace && workspace_bytes >= tile_need && (uintptr_t)workspace % 256 == 0 &&
                        sm_count_of(dev) > 0 && gemv_tile_applicable(qtype, N, K, tile_m, w, x_bf16);
   static const int wide_min = [] { const char* e = getenv("GGQ_WIDE_MIN"); return e ? atoi(e) : 5; }();
-  const bool wide_ok = k_quant && M >= wide_min && workspace && (uintptr_t)workspace % 256 == 0 && sm_count_of(dev) > 0 &&
+  const bool wide_ok = k_quant && M >= wide_min && wide_pays(qtype, N * (K / ti->block_elems) * (int64_t)ti->block_bytes) && workspace && (uintptr_t)workspace % 256 == 0 && sm_count_of(dev) > 0 &&
                        workspace_bytes >= gemv_wide_workspace_bytes(qtype, N, K, M, sm_count_of(dev)) &&
                        gemv_wide_applicable(qtype, N, K, M, w, x_bf16);
   if (wide_ok) {
@@ -276,8 +289,12 @@ extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, 
   if (ti->needs_tables && !tab)
     return fail(GGQ_NO_TABLES, "ggq_gemm: call ggq_set_tables(%d, ...) before using qtype %d", dev, qtype);
   cudaError_t err;
-  static const bool tf32_only = [] { const char* e = getenv("GGQ_GEMM_TF32"); return e && e[0] == '1'; }();
-  static const int wide_max = [] { const char* e = getenv("GGQ_WIDE_GEMM_MAX"); return e ? atoi(e) : 128; }();
+  // kernel choice can be pinned from the environment (read on every call, so a test can switch between kernels):
+  // GGQ_GEMM_TF32=1 keeps to the tf32 kernel, GGQ_WIDE_GEMM_MAX=<rows> bounds the batch the batch-major kernel takes
+  const char* env_tf32 = getenv("GGQ_GEMM_TF32");
+  const char* env_wide = getenv("GGQ_WIDE_GEMM_MAX");
+  const bool tf32_only = env_tf32 && env_tf32[0] == '1';
+  const int wide_max = env_wide ? atoi(env_wide) : 128;
   const int wide_slice = gemv_wide_max_batch();
   const int y_item = y_dtype == GGQ_F32 ? 4 : 2;
   if (!tf32_only && M <= wide_max && workspace && (uintptr_t)workspace % 256 == 0 &&

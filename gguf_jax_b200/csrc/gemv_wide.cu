@@ -55,6 +55,12 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// the same with a zero C operand: starts a fresh accumulator tile without clearing registers first
+__device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
 __device__ __forceinline__ uint32_t lds_u32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
 __device__ __forceinline__ uint2 lds_v2(uint32_t a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
 __device__ __forceinline__ uint4 lds_v4(uint32_t a) {
@@ -130,6 +136,8 @@ template <class F, int XR>
 __global__ void __launch_bounds__(256)
 prepare_kernel(const __nv_bfloat16* __restrict__ x, int K, int M, uint8_t* __restrict__ xp, uint8_t* __restrict__ xo, int* __restrict__ S_col) {
   __shared__ int s_max;
+  pdl_wait();            // x may be the previous kernel's output, and the previous launch may still read the staged copy
+  pdl_trigger();         // the multiply kernel may start fetching weights
   const int col = blockIdx.x, tid = threadIdx.x;
   const int SB = K / 256;
   const bool real = col < M;
@@ -211,8 +219,7 @@ __device__ __forceinline__ void group_mma2(float (&acc)[NT][4], uint32_t a00, ui
 #pragma unroll
   for (int nt = 0; nt < NT; nt++) {
     const uint4 xv = lds_v4(xq + nt * (8 * 64));
-    acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-    mma16816(acc[nt], a00, a01, a10, a11, xv.x, xv.y);
+    mma16816_first(acc[nt], a00, a01, a10, a11, xv.x, xv.y);
     mma16816(acc[nt], a20, a21, a30, a31, xv.z, xv.w);
   }
 }
@@ -264,8 +271,8 @@ __device__ __forceinline__ void block_q4k(uint32_t blk0, uint32_t blk1, int g, i
 #pragma unroll
   for (int nt = 0; nt < NT; nt++) {
     const uint4 ov = lds_v4(xo + nt * (8 * 64));
-    float a2[4] = {0.f, 0.f, 0.f, 0.f};
-    mma16816(a2, ma0, ma1, mb0, mb1, ov.x, ov.y);
+    float a2[4];
+    mma16816_first(a2, ma0, ma1, mb0, mb1, ov.x, ov.y);
     mma16816(a2, ma0, ma1, mb0, mb1, ov.z, ov.w);
     out[nt][0] = fmaf(d0, ts[nt][0], out[nt][0]); out[nt][0] = fmaf(nm0, a2[0], out[nt][0]);
     out[nt][1] = fmaf(d0, ts[nt][1], out[nt][1]); out[nt][1] = fmaf(nm0, a2[1], out[nt][1]);
@@ -325,8 +332,8 @@ __device__ __forceinline__ void block_q5k(uint32_t blk0, uint32_t blk1, int g, i
 #pragma unroll
   for (int nt = 0; nt < NT; nt++) {
     const uint4 ov = lds_v4(xo + nt * (8 * 64));
-    float a2[4] = {0.f, 0.f, 0.f, 0.f};
-    mma16816(a2, ma0, ma1, mb0, mb1, ov.x, ov.y);
+    float a2[4];
+    mma16816_first(a2, ma0, ma1, mb0, mb1, ov.x, ov.y);
     mma16816(a2, ma0, ma1, mb0, mb1, ov.z, ov.w);
     out[nt][0] = fmaf(d0, ts[nt][0], out[nt][0]); out[nt][0] = fmaf(nm0, a2[0], out[nt][0]);
     out[nt][1] = fmaf(d0, ts[nt][1], out[nt][1]); out[nt][1] = fmaf(nm0, a2[1], out[nt][1]);
@@ -379,8 +386,8 @@ __device__ __forceinline__ void block_q6k(uint32_t blk0, uint32_t blk1, int g, i
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
           const uint2 xv = lds_v2(xl + q * (XR * 32) + nt * (8 * 32));
-          float acc[4] = {0.f, 0.f, 0.f, 0.f};
-          mma16816(acc, a0, a1, a2, a3, xv.x, xv.y);
+          float acc[4];
+          mma16816_first(acc, a0, a1, a2, a3, xv.x, xv.y);
           ts[nt][0] = fmaf(f0, acc[0], ts[nt][0]); ts[nt][1] = fmaf(f0, acc[1], ts[nt][1]);
           ts[nt][2] = fmaf(f1, acc[2], ts[nt][2]); ts[nt][3] = fmaf(f1, acc[3], ts[nt][3]);
         }
@@ -405,8 +412,8 @@ __device__ __forceinline__ void block_q6k(uint32_t blk0, uint32_t blk1, int g, i
   for (int nt = 0; nt < NT; nt++) {
     const uint4 ov = lds_v4(xo + nt * (8 * 128));
     const uint2 ol = lds_v2(xo + nt * (8 * 128) + 16);
-    float a2[4] = {0.f, 0.f, 0.f, 0.f};
-    mma16816(a2, ca0, ca1, cb0, cb1, ov.x, ov.y);
+    float a2[4];
+    mma16816_first(a2, ca0, ca1, cb0, cb1, ov.x, ov.y);
     mma16816(a2, ca0, ca1, cb0, cb1, ov.z, ov.w);
     mma16816(a2, ca0, ca1, cb0, cb1, ol.x, ol.y);
     out[nt][0] = fmaf(d0, fmaf(-32.f, a2[0], ts[nt][0]), out[nt][0]);
@@ -457,36 +464,53 @@ gemv_wide_kernel(const uint8_t* __restrict__ w, int N, int K, const uint8_t* __r
   const uint32_t my_ring = smem_base + warp * (depth * geo.wslot_bytes);
   const uint32_t x_ring = smem_base + geo.off_x;
   const int hl = lane >> 4, kl = lane & 15;
-  int issued = 0, slot_i = 0;
-  int rb_i = rb_first, k_i = (int)(s_begin - (int64_t)rb_first * SB);
-  auto issue_next = [&]() {
-    if (issued < n_steps) {
-      // this warp's 16 rows of superblock k_i: a half-warp copies one row (the 16-byte aligned window around the block)
-      const int row0 = rb_i * kBlockRows + warp * 16;
+  // weights and activations are issued by separate cursors: the first weight copies go out before this kernel
+  // waits for its predecessor (the weights are immutable), the activations only after it
+  int w_issued = 0, w_slot = 0, w_rb = rb_first, w_k = (int)(s_begin - (int64_t)rb_first * SB);
+  auto issue_w = [&]() {
+    if (w_issued < n_steps) {
+      // this warp's 16 rows of superblock w_k: a half-warp copies one row (the 16-byte aligned window around the block)
+      const int row0 = w_rb * kBlockRows + warp * 16;
       if (row0 < N) {
-        const int boff = k_i * F::kTs;
+        const int boff = w_k * F::kTs;
         const int pieces = ((boff & 15) + F::kTs + 15) >> 4;
-        const uint8_t* src0 = w + (boff & ~15) + 16 * kl;
-        const uint32_t dst0 = my_ring + slot_i * geo.wslot_bytes + hl * F::kPitch + 16 * kl;
+        const uint32_t dst0 = my_ring + w_slot * geo.wslot_bytes + hl * F::kPitch + 16 * kl;
         if (kl < pieces) {
+          if (row0 + 16 <= N) {
+            const uint8_t* src = w + (int64_t)(row0 + hl) * row_bytes + ((boff & ~15) + 16 * kl);
 #pragma unroll
-          for (int i = 0; i < 8; i++)
-            cp_async16(dst0 + i * (2 * F::kPitch), src0 + (int64_t)min(row0 + 2 * i + hl, N - 1) * row_bytes);
+            for (int i = 0; i < 8; i++) { cp_async16(dst0 + i * (2 * F::kPitch), src); src += 2 * row_bytes; }
+          } else {        // ragged last rows: rows past the end repeat row N - 1 (multiplied, never stored)
+            const uint8_t* src0 = w + ((boff & ~15) + 16 * kl);
+#pragma unroll
+            for (int i = 0; i < 8; i++) cp_async16(dst0 + i * (2 * F::kPitch), src0 + (int64_t)min(row0 + 2 * i + hl, N - 1) * row_bytes);
+          }
         }
       }
-      // the step's activations, the same for every warp
-      const uint32_t xdst = x_ring + slot_i * geo.xstage_bytes;
-      const uint8_t* xsrc = xp + (int64_t)k_i * kStageX;
-      for (int q = tid; q < kStageX / 16; q += kThreads) cp_async16(xdst + q * 16, xsrc + q * 16);
-      const uint8_t* osrc = xo + (int64_t)k_i * kStageO;
-      for (int q = tid; q < kStageO / 16; q += kThreads) cp_async16(xdst + kStageX + q * 16, osrc + q * 16);
-      ++issued;
-      if (++slot_i == depth) slot_i = 0;
-      if (++k_i == SB) { k_i = 0; ++rb_i; }
+      ++w_issued;
+      if (++w_slot == depth) w_slot = 0;
+      if (++w_k == SB) { w_k = 0; ++w_rb; }
     }
-    cp_async_commit();
   };
-  for (int d = 0; d < depth - 1; d++) issue_next();
+  int x_issued = 0, x_slot = 0, x_k = w_k;
+  auto issue_x = [&]() {
+    if (x_issued < n_steps) {
+      // the step's activations, the same for every warp
+      const uint32_t xdst = x_ring + x_slot * geo.xstage_bytes;
+      const uint8_t* xsrc = xp + (int64_t)x_k * kStageX;
+      for (int q = tid; q < kStageX / 16; q += kThreads) cp_async16(xdst + q * 16, xsrc + q * 16);
+      const uint8_t* osrc = xo + (int64_t)x_k * kStageO;
+      for (int q = tid; q < kStageO / 16; q += kThreads) cp_async16(xdst + kStageX + q * 16, osrc + q * 16);
+      ++x_issued;
+      if (++x_slot == depth) x_slot = 0;
+      if (++x_k == SB) x_k = 0;
+    }
+  };
+  for (int d = 0; d < depth - 1; d++) issue_w();
+  pdl_wait();            // the prepare kernel's output (and the previous launch's use of the scratch) is behind us
+  pdl_trigger();
+  for (int d = 0; d < depth - 1; d++) { issue_x(); cp_async_commit(); }
+  auto issue_next = [&]() { issue_w(); issue_x(); cp_async_commit(); };
 
   float out[NT][4];
 #pragma unroll
@@ -629,11 +653,13 @@ static cudaError_t launch(const Geo& geo, int grid, cudaStream_t st, const uint8
     attr_done[dev].store(true, std::memory_order_release);
   }
   constexpr int XR = 8 * NT;
-  prepare_kernel<F, XR><<<XR, 256, 0, st>>>((const __nv_bfloat16*)x, K, M, ws + l.xp, ws + l.xo, reinterpret_cast<int*>(ws + l.scol));
-  gemv_wide_kernel<F, NT><<<grid, kThreads, geo.total, st>>>(w, N, K, ws + l.xp, ws + l.xo, reinterpret_cast<const int*>(ws + l.scol), M, y,
-                                                            y_dtype, reinterpret_cast<int*>(ws + kWsCounterOffset),
-                                                            reinterpret_cast<float*>(ws + l.slots), geo);
-  return cudaPeekAtLastError();
+  cudaError_t err = launch_pdl(prepare_kernel<F, XR>, XR, 256, 0, st, (const __nv_bfloat16*)x, K, M, ws + l.xp, ws + l.xo,
+                               reinterpret_cast<int*>(ws + l.scol));
+  if (err != cudaSuccess) return err;
+  err = launch_pdl(gemv_wide_kernel<F, NT>, grid, kThreads, (size_t)geo.total, st, w, N, K, (const uint8_t*)(ws + l.xp),
+                   (const uint8_t*)(ws + l.xo), reinterpret_cast<const int*>(ws + l.scol), M, y, y_dtype,
+                   reinterpret_cast<int*>(ws + kWsCounterOffset), reinterpret_cast<float*>(ws + l.slots), geo);
+  return err != cudaSuccess ? err : cudaPeekAtLastError();
 }
 
 template <class F>

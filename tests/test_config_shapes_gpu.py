@@ -21,7 +21,8 @@ SHAPES_8B = [("q", QT.Q5_K, 4096, 4096), ("k", QT.Q5_K, 1024, 4096), ("gate", QT
              ("down", QT.Q6_K, 4096, 14336)]
 
 
-def check(product, name, qt, n, k, m, rows=48):
+def check(product, name, qt, n, k, m):
+    rows = max(48, -(-768 // m))          # enough bf16 outputs for the L2 figure to be a statistic
     w = synth.make_weight_on_device(n, k, qt, seed=n + k, device="cuda")
     x = torch.from_numpy(synth.make_x(m, k, seed=m)).cuda().to(torch.bfloat16)
     y = product(x, w)
@@ -30,7 +31,10 @@ def check(product, name, qt, n, k, m, rows=48):
     idx = torch.from_numpy(pick).cuda()
     ref = O.c_matmul(O.bf16_bits(x.float().cpu().numpy()), w.data[idx].cpu().numpy(), qt)
     got = y.float()[:, idx].cpu().numpy()
-    assert O.rel_l2(got, ref) <= 2e-3, (name, qt.name, n, k, m)
+    # above the router's cap `matmul` decodes the weight to bf16 (as the reference's fallback does) before the library
+    # GEMM, which adds the weights' own rounding: twice the bar of the fused route
+    fused = product is not gj.matmul or m <= gj.fused_batch_limit(w)
+    assert O.rel_l2(got, ref) <= (2e-3 if fused else 4e-3), (name, qt.name, n, k, m)
     np.testing.assert_allclose(got, ref, rtol=1e-2, atol=1e-2 * np.abs(ref).max())
 
 

@@ -18,6 +18,12 @@ pytestmark = pytest.mark.gpu
 CODE_TYPES = [QT.Q4_K, QT.Q5_K, QT.Q6_K]
 
 
+@pytest.fixture(autouse=True)
+def _tcgen05_kernel_for_every_batch(monkeypatch):
+    # up to 128 rows ggq_gemm would otherwise hand these formats to the batch-major mma.sync kernel
+    monkeypatch.setenv("GGQ_WIDE_GEMM_MAX", "0")
+
+
 def run(x, wb, qtype, out_dtype=torch.float32):
     n, k = wb.shape[0], x.shape[1]
     w = gj.QuantizedArray.from_bytes(wb, qtype, shape=(n, k), device="cuda")
