@@ -14,10 +14,10 @@
 // superblock: A = the per-group integers (exact codes), B = the per-group sums of x split into three
 // bf16 terms (exact to 24 bits).
 //
-// Work split.  A CTA (16 warps) takes row blocks of 256 rows -- warp w the rows 16 w .. 16 w + 15 --
-// and walks along K one superblock per step; all steps of the launch (row block major) are dealt to
-// the CTAs as equal contiguous ranges.  A row block cut by a range boundary is finished by the last
-// CTA to arrive: each contributor leaves its 256 x M partial sums in one of its two scratch slots,
+// Work split.  A CTA (8 warps, two CTAs per SM so that one's barriers and dependent chains overlap the other's
+// work) takes row blocks of 128 rows -- warp w the rows 16 w .. 16 w + 15 -- and walks along K one superblock
+// per step; all steps of the launch (row block major) are dealt to the CTAs as equal contiguous ranges.  A row block cut by a range boundary is finished by the last
+// CTA to arrive: each contributor leaves its 128 x M partial sums in one of its two scratch slots,
 // bumps the row block's counter, and the last one adds the slots in CTA order (deterministic).
 // The activations of a step are the same for all warps: a separate launch (prepare kernel) writes
 // them once, already in B-fragment order, and the CTAs copy one superblock's worth per step into a
@@ -32,7 +32,8 @@
 namespace ggq {
 namespace wide {
 
-constexpr int kWarps = 16;
+constexpr int kWarps = 8;
+constexpr int kCtasPerSm = 2;
 constexpr int kThreads = kWarps * 32;
 constexpr int kBlockRows = 16 * kWarps;          // rows of a row block
 constexpr int kSmemLimit = 232448;
@@ -442,7 +443,7 @@ __device__ __forceinline__ int cta_of_step(int64_t s, int64_t S, int G) {
 }
 
 template <class F, int NT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gemv_wide_kernel(const uint8_t* __restrict__ w, int N, int K, const uint8_t* __restrict__ xp, const uint8_t* __restrict__ xo,
                  const int* __restrict__ S_col, int M, void* __restrict__ y, int y_dtype, int* __restrict__ counters,
                  float* __restrict__ slots, const Geo geo) {
@@ -619,7 +620,7 @@ static bool plan(const FormatInfo& fi, int64_t N, int64_t K, int M, Geo* geo) {
   g.wslot_bytes = 16 * fi.pitch;
   g.xstage_bytes = XR * (512 + fi.off_bytes);
   const int per_depth = kWarps * g.wslot_bytes + g.xstage_bytes;
-  g.depth = std::min(4, (kSmemLimit - 1024) / per_depth);
+  g.depth = std::min(4, (kSmemLimit / kCtasPerSm - 1024) / per_depth);
   if (g.depth < 2) return false;
   g.off_x = kWarps * g.depth * g.wslot_bytes;
   g.total = g.off_x + g.depth * g.xstage_bytes;
@@ -636,7 +637,7 @@ static WsLayout ws_layout(const FormatInfo& fi, int64_t K, int M, int sm_count) 
   l.xp = p; p += (size_t)SB * XR * 512;
   l.xo = p; p += (size_t)SB * XR * fi.off_bytes;
   l.scol = p; p += 256;
-  l.slots = p; p += (size_t)sm_count * 2 * kBlockRows * XR * sizeof(float);
+  l.slots = p; p += (size_t)sm_count * kCtasPerSm * 2 * kBlockRows * XR * sizeof(float);
   l.total = (p + 255) / 256 * 256;
   return l;
 }
@@ -648,7 +649,7 @@ static cudaError_t launch(const Geo& geo, int grid, cudaStream_t st, const uint8
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_wide_kernel<F, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit - 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemv_wide_kernel<F, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit / kCtasPerSm - 1024);
     if (e != cudaSuccess) return e;
     attr_done[dev].store(true, std::memory_order_release);
   }
@@ -706,7 +707,7 @@ cudaError_t gemv_wide(int qtype, const uint8_t* w, int64_t N, int64_t K, const v
   const WsLayout l = ws_layout(fi, K, M, sm_count);
   if (!ws || ws_bytes < l.total || (uintptr_t)ws % 256) return cudaErrorInvalidValue;
   if (kWsCounterOffset + (size_t)geo.RB * sizeof(int) > kWsGemmPartialOffset) return cudaErrorInvalidValue;
-  const int grid = (int)std::min<int64_t>(sm_count, geo.S);
+  const int grid = (int)std::min<int64_t>((int64_t)sm_count * kCtasPerSm, geo.S);
   const int NT = tiles_of(M);
   uint8_t* base = reinterpret_cast<uint8_t*>(ws);
   switch (qtype) {
