@@ -234,9 +234,8 @@ __device__ __forceinline__ void block_q4k(uint32_t blk0, uint32_t blk1, int g, i
   const uint32_t mn0[2] = {h0.z & 0x3F3F3F3Fu, ((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u)};
   const uint32_t sc1[2] = {h1.y & 0x3F3F3F3Fu, (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u)};
   const uint32_t mn1[2] = {h1.z & 0x3F3F3F3Fu, ((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u)};
-  float ts[NT][4];
-#pragma unroll
-  for (int nt = 0; nt < NT; nt++) ts[nt][0] = ts[nt][1] = ts[nt][2] = ts[nt][3] = 0.f;
+  const __half2 dd0 = *reinterpret_cast<const __half2*>(&h0.x), dd1 = *reinterpret_cast<const __half2*>(&h1.x);
+  const float d0 = __low2float(dd0), nm0 = -__high2float(dd0), d1 = __low2float(dd1), nm1 = -__high2float(dd1);
   const uint32_t xl = xs + (g * 4 + t) * 16;
 #pragma unroll
   for (int p = 0; p < 4; p++) {
@@ -253,10 +252,11 @@ __device__ __forceinline__ void block_q4k(uint32_t blk0, uint32_t blk1, int g, i
                        (j & 3) == 2 ? byte_to_float<2>(sc0[j >> 2]) : byte_to_float<3>(sc0[j >> 2]);
       const float s1 = (j & 3) == 0 ? byte_to_float<0>(sc1[j >> 2]) : (j & 3) == 1 ? byte_to_float<1>(sc1[j >> 2]) :
                        (j & 3) == 2 ? byte_to_float<2>(sc1[j >> 2]) : byte_to_float<3>(sc1[j >> 2]);
+      const float ds0 = __fmul_rn(d0, s0), ds1 = __fmul_rn(d1, s1);      // exact: 11 x 6 bits
 #pragma unroll
       for (int nt = 0; nt < NT; nt++) {
-        ts[nt][0] = fmaf(s0, acc[nt][0], ts[nt][0]); ts[nt][1] = fmaf(s0, acc[nt][1], ts[nt][1]);
-        ts[nt][2] = fmaf(s1, acc[nt][2], ts[nt][2]); ts[nt][3] = fmaf(s1, acc[nt][3], ts[nt][3]);
+        out[nt][0] = fmaf(ds0, acc[nt][0], out[nt][0]); out[nt][1] = fmaf(ds0, acc[nt][1], out[nt][1]);
+        out[nt][2] = fmaf(ds1, acc[nt][2], out[nt][2]); out[nt][3] = fmaf(ds1, acc[nt][3], out[nt][3]);
       }
     }
   }
@@ -266,8 +266,6 @@ __device__ __forceinline__ void block_q4k(uint32_t blk0, uint32_t blk1, int g, i
   const uint32_t sel_a = bsel | (4u << 4) | (bsel << 8) | (4u << 12), sel_b = sel_a + 0x0101u;
   const uint32_t ma0 = __byte_perm(mw0, 0u, sel_a), mb0 = __byte_perm(mw0, 0u, sel_b);
   const uint32_t ma1 = __byte_perm(mw1, 0u, sel_a), mb1 = __byte_perm(mw1, 0u, sel_b);
-  const __half2 dd0 = *reinterpret_cast<const __half2*>(&h0.x), dd1 = *reinterpret_cast<const __half2*>(&h1.x);
-  const float d0 = __low2float(dd0), nm0 = -__high2float(dd0), d1 = __low2float(dd1), nm1 = -__high2float(dd1);
   const uint32_t xo = xs + XR * 512 + (g * 4 + t) * 16;
 #pragma unroll
   for (int nt = 0; nt < NT; nt++) {
@@ -275,10 +273,8 @@ __device__ __forceinline__ void block_q4k(uint32_t blk0, uint32_t blk1, int g, i
     float a2[4];
     mma16816_first(a2, ma0, ma1, mb0, mb1, ov.x, ov.y);
     mma16816(a2, ma0, ma1, mb0, mb1, ov.z, ov.w);
-    out[nt][0] = fmaf(d0, ts[nt][0], out[nt][0]); out[nt][0] = fmaf(nm0, a2[0], out[nt][0]);
-    out[nt][1] = fmaf(d0, ts[nt][1], out[nt][1]); out[nt][1] = fmaf(nm0, a2[1], out[nt][1]);
-    out[nt][2] = fmaf(d1, ts[nt][2], out[nt][2]); out[nt][2] = fmaf(nm1, a2[2], out[nt][2]);
-    out[nt][3] = fmaf(d1, ts[nt][3], out[nt][3]); out[nt][3] = fmaf(nm1, a2[3], out[nt][3]);
+    out[nt][0] = fmaf(nm0, a2[0], out[nt][0]); out[nt][1] = fmaf(nm0, a2[1], out[nt][1]);
+    out[nt][2] = fmaf(nm1, a2[2], out[nt][2]); out[nt][3] = fmaf(nm1, a2[3], out[nt][3]);
   }
 }
 
@@ -292,9 +288,8 @@ __device__ __forceinline__ void block_q5k(uint32_t blk0, uint32_t blk1, int g, i
   const uint32_t sc1[2] = {h1.y & 0x3F3F3F3Fu, (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u)};
   const uint32_t mn1[2] = {h1.z & 0x3F3F3F3Fu, ((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u)};
   const uint2 qh0 = lds_v2(blk0 + 16 + 8 * t), qh1 = lds_v2(blk1 + 16 + 8 * t);
-  float ts[NT][4];
-#pragma unroll
-  for (int nt = 0; nt < NT; nt++) ts[nt][0] = ts[nt][1] = ts[nt][2] = ts[nt][3] = 0.f;
+  const __half2 dd0 = *reinterpret_cast<const __half2*>(&h0.x), dd1 = *reinterpret_cast<const __half2*>(&h1.x);
+  const float d0 = __low2float(dd0), nm0 = -__high2float(dd0), d1 = __low2float(dd1), nm1 = -__high2float(dd1);
   const uint32_t xl = xs + (g * 4 + t) * 16;
 #pragma unroll
   for (int p = 0; p < 4; p++) {
@@ -315,10 +310,11 @@ __device__ __forceinline__ void block_q5k(uint32_t blk0, uint32_t blk1, int g, i
                        (j & 3) == 2 ? byte_to_float<2>(sc0[j >> 2]) : byte_to_float<3>(sc0[j >> 2]);
       const float s1 = (j & 3) == 0 ? byte_to_float<0>(sc1[j >> 2]) : (j & 3) == 1 ? byte_to_float<1>(sc1[j >> 2]) :
                        (j & 3) == 2 ? byte_to_float<2>(sc1[j >> 2]) : byte_to_float<3>(sc1[j >> 2]);
+      const float ds0 = __fmul_rn(d0, s0), ds1 = __fmul_rn(d1, s1);      // exact: 11 x 6 bits
 #pragma unroll
       for (int nt = 0; nt < NT; nt++) {
-        ts[nt][0] = fmaf(s0, acc[nt][0], ts[nt][0]); ts[nt][1] = fmaf(s0, acc[nt][1], ts[nt][1]);
-        ts[nt][2] = fmaf(s1, acc[nt][2], ts[nt][2]); ts[nt][3] = fmaf(s1, acc[nt][3], ts[nt][3]);
+        out[nt][0] = fmaf(ds0, acc[nt][0], out[nt][0]); out[nt][1] = fmaf(ds0, acc[nt][1], out[nt][1]);
+        out[nt][2] = fmaf(ds1, acc[nt][2], out[nt][2]); out[nt][3] = fmaf(ds1, acc[nt][3], out[nt][3]);
       }
     }
   }
@@ -327,8 +323,6 @@ __device__ __forceinline__ void block_q5k(uint32_t blk0, uint32_t blk1, int g, i
   const uint32_t sel_a = bsel | (4u << 4) | (bsel << 8) | (4u << 12), sel_b = sel_a + 0x0101u;
   const uint32_t ma0 = __byte_perm(mw0, 0u, sel_a), mb0 = __byte_perm(mw0, 0u, sel_b);
   const uint32_t ma1 = __byte_perm(mw1, 0u, sel_a), mb1 = __byte_perm(mw1, 0u, sel_b);
-  const __half2 dd0 = *reinterpret_cast<const __half2*>(&h0.x), dd1 = *reinterpret_cast<const __half2*>(&h1.x);
-  const float d0 = __low2float(dd0), nm0 = -__high2float(dd0), d1 = __low2float(dd1), nm1 = -__high2float(dd1);
   const uint32_t xo = xs + XR * 512 + (g * 4 + t) * 16;
 #pragma unroll
   for (int nt = 0; nt < NT; nt++) {
@@ -336,10 +330,8 @@ __device__ __forceinline__ void block_q5k(uint32_t blk0, uint32_t blk1, int g, i
     float a2[4];
     mma16816_first(a2, ma0, ma1, mb0, mb1, ov.x, ov.y);
     mma16816(a2, ma0, ma1, mb0, mb1, ov.z, ov.w);
-    out[nt][0] = fmaf(d0, ts[nt][0], out[nt][0]); out[nt][0] = fmaf(nm0, a2[0], out[nt][0]);
-    out[nt][1] = fmaf(d0, ts[nt][1], out[nt][1]); out[nt][1] = fmaf(nm0, a2[1], out[nt][1]);
-    out[nt][2] = fmaf(d1, ts[nt][2], out[nt][2]); out[nt][2] = fmaf(nm1, a2[2], out[nt][2]);
-    out[nt][3] = fmaf(d1, ts[nt][3], out[nt][3]); out[nt][3] = fmaf(nm1, a2[3], out[nt][3]);
+    out[nt][0] = fmaf(nm0, a2[0], out[nt][0]); out[nt][1] = fmaf(nm0, a2[1], out[nt][1]);
+    out[nt][2] = fmaf(nm1, a2[2], out[nt][2]); out[nt][3] = fmaf(nm1, a2[3], out[nt][3]);
   }
 }
 

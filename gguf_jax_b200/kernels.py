@@ -59,8 +59,11 @@ def _check(x: torch.Tensor, w: QuantizedArray, qtypes=None) -> tuple[int, int]:
 
 
 def fused_matmul(x: torch.Tensor, w: QuantizedArray, *, out_dtype=torch.bfloat16) -> torch.Tensor:
-    """``x @ w.T`` through the fused kernels, whatever the batch: the small-batch kernel up
-    to ``gemv_max_batch()``, the tensor-core kernel above it."""
+    """``x @ w.T`` through the fused kernels, whatever the batch: ``ggq_gemv`` up to
+    ``gemv_max_batch()`` rows (tuned batch-1, tiled, batch-major or small-weight MMA kernel, chosen
+    by the library per format, batch and weight size), ``ggq_gemm`` above it (Q4_K / Q5_K / Q6_K:
+    the batch-major kernel in slices of 32 rows up to 128 rows, then the integer-code tcgen05
+    kernel; other formats: the tf32 tcgen05 kernel)."""
     n_rows, k_dim = _check(x, w)
     dev = _backend.require_cuda(w.data, f"fused matmul ({w.qtype.name})")
     if x.device != w.data.device:
@@ -115,19 +118,22 @@ def matmul_q6_k(x, w):
 
 
 def matmul_iq4_xs(x, w):
-    """IQ4_XS fused multiply (src/gguf_jax/cute/iq4_xs.py:146-175)."""
+    """IQ4_XS fused multiply (src/gguf_jax/cute/iq4_xs.py:146-175): the tiled kernel, whose
+    16-entry code book is applied with byte permutes on register-resident tables."""
     _check(x, w, (QT.IQ4_XS,))
     return fused_matmul(x, w)
 
 
 def matmul_lowbit(x, w):
-    """Fused multiply for the eight low-bit types (src/gguf_jax/cute/lowbit.py:675-712)."""
+    """Fused multiply for the eight low-bit types (src/gguf_jax/cute/lowbit.py:675-712): the
+    tiled kernel with the format's grid in shared memory and exact integer codes on the tensor cores."""
     _check(x, w, LOWBIT_TYPES)
     return fused_matmul(x, w)
 
 
 def gemm_q4_k(x, w):
-    """Q4_K tensor-core multiply for larger batches (src/gguf_jax/cute/q4_k_gemm.py:369-391)."""
+    """Q4_K tensor-core multiply for larger batches (src/gguf_jax/cute/q4_k_gemm.py:369-391);
+    see :func:`fused_matmul` for which kernel a batch gets."""
     _check(x, w, (QT.Q4_K,))
     return fused_matmul(x, w)
 
