@@ -76,6 +76,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&p);
 }
+// o0 += s * a0, o1 += s * a1 as one packed instruction
+__device__ __forceinline__ void fma_pair(float& o0, float& o1, float s, float a0, float a1) {
+  asm("{ .reg .b64 o, a, ss;\n mov.b64 o, {%0, %1};\n mov.b64 a, {%3, %4};\n mov.b64 ss, {%2, %2};\n fma.rn.f32x2 o, ss, a, o;\n mov.b64 {%0, %1}, o; }"
+      : "+f"(o0), "+f"(o1) : "f"(s), "f"(a0), "f"(a1));
+}
 // byte SEL of x as a float, exact: the bits 0x4B0000vv are 2^23 + v
 template <int SEL>
 __device__ __forceinline__ float byte_to_float(uint32_t x) {
@@ -255,8 +260,8 @@ __device__ __forceinline__ void block_q4k(uint32_t blk0, uint32_t blk1, int g, i
       const float ds0 = __fmul_rn(d0, s0), ds1 = __fmul_rn(d1, s1);      // exact: 11 x 6 bits
 #pragma unroll
       for (int nt = 0; nt < NT; nt++) {
-        out[nt][0] = fmaf(ds0, acc[nt][0], out[nt][0]); out[nt][1] = fmaf(ds0, acc[nt][1], out[nt][1]);
-        out[nt][2] = fmaf(ds1, acc[nt][2], out[nt][2]); out[nt][3] = fmaf(ds1, acc[nt][3], out[nt][3]);
+        fma_pair(out[nt][0], out[nt][1], ds0, acc[nt][0], acc[nt][1]);
+        fma_pair(out[nt][2], out[nt][3], ds1, acc[nt][2], acc[nt][3]);
       }
     }
   }
@@ -313,8 +318,8 @@ __device__ __forceinline__ void block_q5k(uint32_t blk0, uint32_t blk1, int g, i
       const float ds0 = __fmul_rn(d0, s0), ds1 = __fmul_rn(d1, s1);      // exact: 11 x 6 bits
 #pragma unroll
       for (int nt = 0; nt < NT; nt++) {
-        out[nt][0] = fmaf(ds0, acc[nt][0], out[nt][0]); out[nt][1] = fmaf(ds0, acc[nt][1], out[nt][1]);
-        out[nt][2] = fmaf(ds1, acc[nt][2], out[nt][2]); out[nt][3] = fmaf(ds1, acc[nt][3], out[nt][3]);
+        fma_pair(out[nt][0], out[nt][1], ds0, acc[nt][0], acc[nt][1]);
+        fma_pair(out[nt][2], out[nt][3], ds1, acc[nt][2], acc[nt][3]);
       }
     }
   }
@@ -381,8 +386,8 @@ __device__ __forceinline__ void block_q6k(uint32_t blk0, uint32_t blk1, int g, i
           const uint2 xv = lds_v2(xl + q * (XR * 32) + nt * (8 * 32));
           float acc[4];
           mma16816_first(acc, a0, a1, a2, a3, xv.x, xv.y);
-          ts[nt][0] = fmaf(f0, acc[0], ts[nt][0]); ts[nt][1] = fmaf(f0, acc[1], ts[nt][1]);
-          ts[nt][2] = fmaf(f1, acc[2], ts[nt][2]); ts[nt][3] = fmaf(f1, acc[3], ts[nt][3]);
+          fma_pair(ts[nt][0], ts[nt][1], f0, acc[0], acc[1]);
+          fma_pair(ts[nt][2], ts[nt][3], f1, acc[2], acc[3]);
         }
       }
     }
