@@ -533,15 +533,14 @@ cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
 // ggq_gemv_q4k_static: the same batch-1 Q4_K kernel for callers that cannot hand over scratch.
 //
 // Some hosts of this library are not allowed to allocate device memory around a call: a
-// custom-call handler whose framework owns every buffer and passes only operands and results,
-// code running between cudaStreamBeginCapture and EndCapture (where cudaMalloc is an error), a
+// custom-call handler whose framework owns every buffer and passes only operands and results, a
 // serving loop with a fixed memory plan.  For them the partial-sum slots and arrival counters
 // live in the file-scope device array below instead of a caller buffer.  Every GPU that loads
 // the library carries these 192 KB until the process exits.
 //
 // In host code the array's name is only a host-side handle; the device address is obtained per
 // device with cudaGetSymbolAddress (with that device current) the first time the entry point
-// runs there, which is why that first call should be made outside any stream capture.
+// runs there (a synchronous runtime query).
 // All calls on a device share the one array: calls whose kernels may overlap on the GPU
 // (different streams without an ordering between them) would mix their partial sums and must be
 // serialised by the caller.  The counters are cleared on the stream before every launch, so a

@@ -180,15 +180,14 @@ int32_t ggq_gemv_sharded_tagged(int32_t qtype, const void* w, int64_t N_local, i
 
 /* Batch-1 Q4_K multiply that needs no scratch from the caller and allocates nothing.
  * No counterpart in the reference.  It exists for hosts that cannot allocate device memory
- * around a call: a custom-call handler whose framework owns every buffer, code between
- * cudaStreamBeginCapture and cudaStreamEndCapture (cudaMalloc is an error there), a serving
- * loop with a fixed memory plan.  The scratch of ggq_gemv lives in a 192 KB device array
+ * around a call: a custom-call handler whose framework owns every buffer, a serving loop
+ * with a fixed memory plan.  The scratch of ggq_gemv lives in a 192 KB device array
  * built into the library (held by every GPU that loads it until the process exits), which
  * bounds the weight to N <= 524288 rows; K as for the Q4_K path of ggq_gemv (multiple of 256,
  * activations resident in shared memory), w and x 16-byte aligned, M = 1.  Larger N or an
  * unsupported K returns GGQ_BAD_SHAPE with the limit in ggq_last_error().
- * The first call on a device looks up the array's device address; make that first call
- * outside any stream capture.  All calls on one device share the array: calls whose kernels
+ * The first call on a device looks up the array's device address (a synchronous runtime
+ * query).  All calls on one device share the array: calls whose kernels
  * could overlap on the GPU (unordered streams) must be serialised by the caller.  The result
  * is identical to ggq_gemv on the same inputs. */
 int32_t ggq_gemv_q4k_static(const void* w, int64_t N, int64_t K, const void* x_bf16, void* y,

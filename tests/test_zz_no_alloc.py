@@ -1,8 +1,7 @@
 """The scratch-free Q4_K entry point, ggq_gemv_q4k_static.
 
 It serves callers that may not allocate device memory around a call (a framework's custom-call
-handler that only receives operands and results, code inside a stream capture, a serving loop
-with a fixed memory plan): the partial sums and arrival counters that ggq_gemv keeps in a
+handler that only receives operands and results, a serving loop with a fixed memory plan): the partial sums and arrival counters that ggq_gemv keeps in a
 caller-provided buffer sit in a device array built into the library instead.  The test drives it
 through the C ABI twice in a row -- the second call reuses whatever the first left in the shared
 array -- and requires the same float32 result as ggq_gemv, bit for bit (same kernel, same split).
