@@ -533,6 +533,23 @@ def extra_legs(dev) -> dict:
         del ws
         torch.cuda.empty_cache()
     out["dequantize_16384x8192"] = dec
+
+    # ---- the reference's own CPU-runnable case: Q4_K 4096 x 4096, decode bit-exact and fused product at batch 1
+    qt = QT["Q4_K"]
+    n = k = 4096
+    wb = synth.make_weight_bytes(n, k, qt, seed=4096)
+    ws = [gj.QuantizedArray.from_bytes(wb, qt, shape=(n, k), device=dev)] + \
+         [synth.make_weight_on_device(n, k, qt, seed=4097 + c, device=dev) for c in range(31)]       # 32 x 9.4 MB > 2 x L2
+    x = x_of(1, k, 1)
+    dense = ws[0].dequantize(torch.float32).cpu().numpy()
+    ref_dense = O.c_dequantize(wb, qt)
+    us = _graph_us([(lambda w=w: gj.matmul(x, w)) for w in ws * 2])
+    y = gj.matmul(x, ws[0]).float().cpu().numpy()
+    ref = O.c_matmul(O.bf16_bits(x.float().cpu().numpy()), wb, qt)
+    moved = wbytes(qt, n, k) + 2 * k + 2 * n
+    out["q4_k_4096x4096_m1"] = {"us": us, "gbs": moved / us / 1e3, "frac_of_measured_hbm": moved / us / 1e3 / peak,
+                                "decode_bit_exact": bool((dense.view(np.uint32) == ref_dense.view(np.uint32)).all()),
+                                "rel_l2_all_rows": O.rel_l2(y, ref)}
     return out
 
 

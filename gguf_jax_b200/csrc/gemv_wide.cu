@@ -222,12 +222,14 @@ template <int NT>
 __device__ __forceinline__ void group_mma2(float (&acc)[NT][4], uint32_t a00, uint32_t a01, uint32_t a10, uint32_t a11,
                                            uint32_t a20, uint32_t a21, uint32_t a30, uint32_t a31, uint32_t xq) {
   // a{r}{row}: register r (0..3) of the lane's octet for row g (0) / g + 8 (1); xq: this lane's piece of column tile 0
+  // all first halves, then all second halves: the two MMAs of a column tile depend on each other, the tiles do not
+  uint4 xv[NT];
 #pragma unroll
-  for (int nt = 0; nt < NT; nt++) {
-    const uint4 xv = lds_v4(xq + nt * (8 * 64));
-    mma16816_first(acc[nt], a00, a01, a10, a11, xv.x, xv.y);
-    mma16816(acc[nt], a20, a21, a30, a31, xv.z, xv.w);
-  }
+  for (int nt = 0; nt < NT; nt++) xv[nt] = lds_v4(xq + nt * (8 * 64));
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++) mma16816_first(acc[nt], a00, a01, a10, a11, xv[nt].x, xv[nt].y);
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++) mma16816(acc[nt], a20, a21, a30, a31, xv[nt].z, xv[nt].w);
 }
 
 template <int NT>

@@ -97,6 +97,17 @@ def test_batch_rows_of_different_magnitude(qtype):
     assert not np.any(got[11])
 
 
+def test_shortest_rows():
+    # one and two superblocks per row (Q6_K rows are 16-byte aligned only from eight superblocks on)
+    for qtype, n, k in [(QT.Q4_K, 64, 256), (QT.Q4_K, 700, 512), (QT.Q5_K, 300, 512), (QT.Q5_K, 40, 256), (QT.Q6_K, 130, 2048)]:
+        wb = synth.make_weight_bytes(n, k, qtype, seed=k)
+        w = on_device(wb, qtype, n, k)
+        for m in (3, 20):
+            xb = synth.make_x(m, k, seed=m)
+            ref = O.c_matmul(O.bf16_bits(xb), wb, qtype)
+            assert O.rel_l2(wide_direct(to_x(xb), w, qtype, n, k).cpu().numpy(), ref) <= 2e-5, (qtype.name, n, k, m)
+
+
 def test_repeatable_and_independent_of_other_batch_rows():
     qt, (n, k) = QT.Q4_K, (1100, 6144)
     wb = synth.make_weight_bytes(n, k, qt, seed=11)
