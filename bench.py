@@ -348,22 +348,22 @@ def decode_leg(world: int, rank: int, dev, batch: int = 1, route: str = "fused")
         got = y_full.float().reshape(batch, -1)[:, rank * rows_local + torch.from_numpy(pick).to(dev)].cpu().numpy()
         return O.rel_l2(got, ref)
 
-    errs = [product_error(value(last_hidden[0]), head, lv, 64, 7)]
+    errs = [product_error(value(last_hidden[0]), head, lv, 128, 7)]
     ws0 = layers[0]
     h0 = x0
     qk = value(mm(x0, ws0[0]))
-    errs.append(product_error(h0, ws0[0], qk, 32, 11))
+    errs.append(product_error(h0, ws0[0], qk, 128, 11))
     vv = value(mm(x0, ws0[1]))
-    errs.append(product_error(h0, ws0[1], vv, 32, 12))
+    errs.append(product_error(h0, ws0[1], vv, 128, 12))
     qk_h = mm(x0, ws0[0])
     o_h = mm(qk_h, ws0[2])
     o_v = value(o_h)
     gu_h = mm(o_h, ws0[3])
     gu_v = value(gu_h)
     d_v = value(mm(gu_h, ws0[4]))
-    errs.append(product_error(qk, ws0[2], o_v, 32, 13))
-    errs.append(product_error(o_v, ws0[3], gu_v, 32, 14))
-    errs.append(product_error(gu_v, ws0[4], d_v, 32, 15))
+    errs.append(product_error(qk, ws0[2], o_v, 128, 13))
+    errs.append(product_error(o_v, ws0[3], gu_v, 128, 14))
+    errs.append(product_error(gu_v, ws0[4], d_v, 128, 15))
     head_err = torch.tensor([errs[0], max(errs)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(head_err, op=dist.ReduceOp.MAX)
@@ -380,7 +380,7 @@ def decode_leg(world: int, rank: int, dev, batch: int = 1, route: str = "fused")
             "logits_finite": finite, "logits_rms": float(lv.pow(2).mean().sqrt()), "device_status": device_status(),
             "parity": {"lm_head_rel_l2_vs_oracle": float(head_err[0].item()),
                        "worst_of_first_layer_and_head_rel_l2_vs_oracle": float(head_err[1].item()),
-                       "rows": (64 + 5 * 32) * world, "bar": 2e-3,
+                       "rows": 6 * 128 * world, "bar": 2e-3,
                        "note": "each product fed with the vector the chain produced; sampled rows of every rank's shard"},
             "checksum": checksum,
             "exchange": exchange,

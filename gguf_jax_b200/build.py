@@ -15,7 +15,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "_obj")
 LIB = os.path.join(HERE, "libggq_b200.so")
 
-SOURCES = ["capi.cu", "dequant.cu", "gemv.cu", "gemv_generic.cu", "gemv_stream.cu", "gemv_q4k.cu", "gemv_q5k.cu", "gemv_q6k.cu", "gemm_tcgen05.cu", "gemv_mma.cu", "gemv_tile.cu", "gemv_wide.cu", "gemm_codes.cu"]
+SOURCES = ["capi.cu", "dequant.cu", "gemv.cu", "gemv_generic.cu", "gemv_stream.cu", "gemv_q4k.cu", "gemv_q5k.cu", "gemv_q6k.cu", "gemm_tcgen05.cu", "gemv_mma.cu", "gemv_tile.cu", "gemv_wide.cu", "gemm_codes.cu", "gemm_bf16w.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++20",

@@ -36,6 +36,8 @@
 // (GGQ_TIMEOUT through ggq_read_status), lets the CTA fall through to the common exit, and
 // the TMEM allocation is always released.
 #define GGQ_DECODE_GENERIC_LOADS   // the decoders read staged blocks from shared memory
+#include <algorithm>
+
 #include "ggq_decode.cuh"
 #include "gemv.cuh"
 
@@ -374,7 +376,13 @@ static cudaError_t launch(const uint8_t* w, int64_t N, int64_t K, const void* x,
   const int tile_m_max = M >= kMaxTileM ? kMaxTileM : ((M + 15) & ~15) < 16 ? 16 : ((M + 15) & ~15);
   const Layout lay(tile_m_max, raw_pitch<QT>());
   if (lay.stages < 2) return cudaErrorInvalidValue;
-  const int smem = lay.total();
+  // Every CTA lays its shared memory out for its own batch tile: the last tile of a batch that is not a multiple of
+  // kMaxTileM is narrower, fits more stages, and can need more bytes than the full tiles do.
+  int smem = lay.total();
+  if (M > kMaxTileM && M % kMaxTileM) {
+    const int last = std::max(16, (M % kMaxTileM + 15) & ~15);
+    smem = std::max(smem, Layout(last, raw_pitch<QT>()).total());
+  }
   static std::atomic<bool> attr_done[64];   // setting the attribute twice is harmless, so a flag per device suffices
   int dev = 0;
   cudaGetDevice(&dev);

@@ -2,6 +2,7 @@
 #include "gemv.cuh"
 
 #include <cstdlib>
+#include <cstring>
 
 using namespace ggq;
 
@@ -31,6 +32,12 @@ inline bool wide_pays(int qtype, int64_t weight_bytes) {
 // The tcgen05 kernels behind ggq_gemm (integer-code and tf32 operands) are slower than both at every
 // batch measured and are reached only by name, above 128 rows or for the other formats.
 constexpr int kWideRouterBatch = 32;
+// Above 32 rows the bf16-weight tcgen05 kernel (gemm_bf16w.cu; the fallback's own precision) is compared with the same
+// fallback: on the large weights it wins up to 256 rows (Q6_K 14336 x 4096: 55 / 60 / 72 us at 64 / 128 / 256 rows against
+// 67 / 68 / 75 us; Q4_K: 42 / 45 / 60 us) and loses from 512 on, where the activations' tile no longer fits one CTA
+// and the weights are decoded once per 256 rows (142 us against 92 us); on weights of a few MB the fallback's library
+// GEMM reads a decoded copy that stays in the L2 and wins from 64 rows on.
+constexpr int kGemmRouterBatch = 256;
 }
 
 extern "C" int32_t ggq_gemv_max_batch(void) { return kGemvMaxBatch; }
@@ -40,7 +47,7 @@ extern "C" int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K) {
   if (!ti || !ti->fused || N <= 0 || K <= 0 || K % ti->block_elems) return 0;
   if (is_k_quant(qtype) && K % 256 == 0 && (K / 256 * ti->block_bytes) % 16 == 0 &&
       wide_pays(qtype, N * (K / 256) * (int64_t)ti->block_bytes) && gemv_wide_applicable(qtype, N, K, kWideRouterBatch, nullptr, nullptr))
-    return kWideRouterBatch;
+    return gemm_bf16w_applicable(qtype, N, K, kGemmRouterBatch) ? kGemmRouterBatch : kWideRouterBatch;
   return kGemvMaxBatch;
 }
 
@@ -67,6 +74,10 @@ extern "C" size_t ggq_workspace_bytes(int32_t qtype, int64_t N, int64_t K, int32
     if (g > need) need = g;
     if (gemm_codes_applicable(qtype, N, K, M)) {
       const size_t c = gemm_codes_workspace_bytes(qtype, N, K, M, sm_count_of(dev));
+      if (c > need) need = c;
+    }
+    if (gemm_bf16w_applicable(qtype, N, K, M)) {
+      const size_t c = gemm_bf16w_workspace_bytes(qtype, N, K, M, sm_count_of(dev));
       if (c > need) need = c;
     }
   }
@@ -289,31 +300,50 @@ extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, 
   if (ti->needs_tables && !tab)
     return fail(GGQ_NO_TABLES, "ggq_gemm: call ggq_set_tables(%d, ...) before using qtype %d", dev, qtype);
   cudaError_t err;
-  // kernel choice can be pinned from the environment (read on every call, so a test can switch between kernels):
-  // GGQ_GEMM_TF32=1 keeps to the tf32 kernel, GGQ_WIDE_GEMM_MAX=<rows> bounds the batch the batch-major kernel takes
-  const char* env_tf32 = getenv("GGQ_GEMM_TF32");
-  const char* env_wide = getenv("GGQ_WIDE_GEMM_MAX");
-  const bool tf32_only = env_tf32 && env_tf32[0] == '1';
-  const int wide_max = env_wide ? atoi(env_wide) : 128;
+  // Kernel choice for Q4_K / Q5_K / Q6_K (the other formats always take the tf32 tcgen05 kernel):
+  //   up to 32 rows     the batch-major mma.sync kernel: exact integer codes, nothing rounded before the output;
+  //   above             the bf16-weight tcgen05 kernel: weights rounded once to bf16, as the reference's GEMM does.
+  // GGQ_GEMM_KERNEL = wide | bf16w | codes | tf32 pins one of them (read on every call, so a test can switch);
+  // a pinned kernel that cannot take the call falls through to the next one in that order.
+  enum { kAuto, kWide, kBf16w, kCodes, kTf32 };
+  int pin = kAuto;
+  if (const char* e = getenv("GGQ_GEMM_KERNEL")) {
+    pin = !strcmp(e, "wide") ? kWide : !strcmp(e, "bf16w") ? kBf16w : !strcmp(e, "codes") ? kCodes : !strcmp(e, "tf32") ? kTf32 : kAuto;
+  }
   const int wide_slice = gemv_wide_max_batch();
   const int y_item = y_dtype == GGQ_F32 ? 4 : 2;
-  if (!tf32_only && M <= wide_max && workspace && (uintptr_t)workspace % 256 == 0 &&
-      workspace_bytes >= gemv_wide_workspace_bytes(qtype, N, K, M < wide_slice ? M : wide_slice, sm_count_of(dev)) &&
-      gemv_wide_applicable(qtype, N, K, M < wide_slice ? M : wide_slice, w, x_bf16)) {
-    // slices of up to 32 batch rows through the exact-code mma.sync kernel: the weight is read once per slice
+  const int sms = sm_count_of(dev);
+  const bool ws_ok = workspace && (uintptr_t)workspace % 256 == 0;
+  const int slice_m = M < wide_slice ? M : wide_slice;
+  const bool can_wide = ws_ok && gemv_wide_applicable(qtype, N, K, slice_m, w, x_bf16) &&
+                        workspace_bytes >= gemv_wide_workspace_bytes(qtype, N, K, slice_m, sms);
+  const bool can_bf16w = ws_ok && gemm_bf16w_applicable(qtype, N, K, M) &&
+                         workspace_bytes >= gemm_bf16w_workspace_bytes(qtype, N, K, M, sms);
+  const bool can_codes = ws_ok && gemm_codes_applicable(qtype, N, K, M) &&
+                         workspace_bytes >= gemm_codes_workspace_bytes(qtype, N, K, M, sms);
+  int pick = kTf32;
+  if (pin == kAuto) pick = (can_wide && M <= wide_slice) ? kWide : can_bf16w ? kBf16w : can_wide ? kWide : can_codes ? kCodes : kTf32;
+  else if (pin == kWide) pick = can_wide ? kWide : can_bf16w ? kBf16w : can_codes ? kCodes : kTf32;
+  else if (pin == kBf16w) pick = can_bf16w ? kBf16w : can_codes ? kCodes : kTf32;
+  else if (pin == kCodes) pick = can_codes ? kCodes : kTf32;
+  if (pick == kWide) {
+    // slices of up to 32 batch rows: the weight is read once per slice
     err = cudaSuccess;
     for (int m0 = 0; m0 < M && err == cudaSuccess; m0 += wide_slice) {
       const int mb = M - m0 < wide_slice ? M - m0 : wide_slice;
       err = gemv_wide(qtype, (const uint8_t*)w, N, K, (const uint8_t*)x_bf16 + (size_t)m0 * K * 2, mb,
-                      (uint8_t*)y + (size_t)m0 * N * y_item, y_dtype, workspace, workspace_bytes, sm_count_of(dev), (cudaStream_t)stream);
+                      (uint8_t*)y + (size_t)m0 * N * y_item, y_dtype, workspace, workspace_bytes, sms, (cudaStream_t)stream);
     }
-  } else if (!tf32_only && gemm_codes_applicable(qtype, N, K, M) && workspace && (uintptr_t)workspace % 256 == 0 &&
-      workspace_bytes >= gemm_codes_workspace_bytes(qtype, N, K, M, sm_count_of(dev)))
-    err = gemm_codes(qtype, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, device_status_word(dev), workspace, workspace_bytes,
-                     sm_count_of(dev), (cudaStream_t)stream);
-  else
-    err = gemm_tf32(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, device_status_word(dev), workspace, workspace_bytes,
-                    sm_count_of(dev), (cudaStream_t)stream);
+  } else if (pick == kBf16w) {
+    err = gemm_bf16w(qtype, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, device_status_word(dev), workspace, workspace_bytes, sms,
+                     (cudaStream_t)stream);
+  } else if (pick == kCodes) {
+    err = gemm_codes(qtype, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, device_status_word(dev), workspace, workspace_bytes, sms,
+                     (cudaStream_t)stream);
+  } else {
+    err = gemm_tf32(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, device_status_word(dev), workspace, workspace_bytes, sms,
+                    (cudaStream_t)stream);
+  }
   if (err != cudaSuccess) return fail(GGQ_LAUNCH_FAILED, "ggq_gemm: %s", cudaGetErrorString(err));
   return GGQ_OK;
 }

@@ -250,6 +250,13 @@ cudaError_t gemm_tf32(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K
                       int y_dtype, const uint8_t* tab, int* status, void* ws, size_t ws_bytes, int sm_count,
                       cudaStream_t st);
 
+// tcgen05 GEMM with the weights decoded to float32 exactly and rounded once to bf16 (the reference's own contract
+// for its tensor-core GEMM), activations used as they are; Q4_K / Q5_K / Q6_K, any M (gemm_bf16w.cu).
+bool gemm_bf16w_applicable(int qtype, int64_t N, int64_t K, int M);
+size_t gemm_bf16w_workspace_bytes(int qtype, int64_t N, int64_t K, int M, int sm_count);
+cudaError_t gemm_bf16w(int qtype, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y, int y_dtype,
+                       int* status, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st);
+
 // Batches of 2 .. 32 rows per launch for Q4_K / Q5_K / Q6_K: all eight MMA columns are batch rows, one MMA
 // (pair) per scale group, float32 scales on the accumulators (gemv_wide.cu).  Needs the workspace.
 int gemv_wide_max_batch();

@@ -85,8 +85,9 @@ int32_t ggq_dequant(int32_t qtype, const void* blocks, int64_t n_blocks, void* o
  * Replaces the key set of _fused() (src/gguf_jax/_matmul.py:52-75). */
 int32_t ggq_has_fused(int32_t qtype);
 
-/* Largest flattened batch M that the fused route accepts for an (N, K) weight of
- * qtype; 0 when there is none.  Replaces the per-kernel caps
+/* Largest flattened batch M for which the fused route (ggq_gemv up to ggq_gemv_max_batch(), ggq_gemm above) is
+ * the faster one for an (N, K) weight of qtype -- 16, or 256 for Q4_K / Q5_K / Q6_K weights of tens of MB; 0 when
+ * there is no fused kernel.  Replaces the per-kernel caps
  * (src/gguf_jax/_matmul.py:60-75, cute/q4_k.py:117-118, cute/lowbit.py:97). */
 int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K);
 
@@ -124,16 +125,17 @@ int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, const void*
                  int32_t M, void* y, int32_t y_dtype, void* workspace,
                  size_t workspace_bytes, void* stream);
 
-/* Same product for larger M on the tcgen05 tensor-core path.  Replaces gemm_q4_k
- * (src/gguf_jax/cute/q4_k_gemm.py:369-391).  Two kernels:
- *   Q4_K / Q5_K / Q6_K with K % 256 == 0 and the workspace: integer-code operands (exact in bf16),
- *     one tensor-memory accumulator per scale group, float32 scales applied after the MMA -- no
- *     rounding of the weight; x is used at its bf16 value; agrees with float32 arithmetic to 2e-5;
- *   any other block qtype (K % 256 == 0), or the above without workspace: blocks decoded to
- *     float32 and multiplied as tf32 (weights rounded to 10 mantissa bits; relative error 1e-3).
- * With few row tiles a launch cuts K into ranges (partials in the workspace, last arriver adds
- * them in a fixed order: results do not depend on timing).  ggq_fused_batch_limit does not count
- * these kernels while they are slower than decode + library GEMM: callers pick ggq_gemm by name. */
+/* The same product for larger M.  Replaces gemm_q4_k (src/gguf_jax/cute/q4_k_gemm.py:369-391).  Kernels:
+ *   Q4_K / Q5_K / Q6_K, K % 256 == 0, rows of a multiple of 16 bytes, with the workspace:
+ *     M <= 32: the batch-major mma.sync kernel of ggq_gemv (exact integer codes, nothing rounded);
+ *     M  > 32: tcgen05 / tensor memory with the weights decoded exactly and rounded once to bf16 -- the
+ *              reference's contract for its GEMM and its fallback (relative error of the result about 2e-3);
+ *   any other block qtype (K % 256 == 0), or the above without workspace: tcgen05 with blocks decoded to float32 and
+ *     multiplied as tf32 (weights rounded to 11 significant bits; relative error about 3e-4).
+ * GGQ_GEMM_KERNEL = wide | bf16w | codes | tf32 in the environment pins one kernel (codes: integer-code tcgen05
+ * operands with one accumulator per scale group, exact but slower).  With few row tiles a launch cuts K into ranges
+ * (partials in the workspace, the last arriver adds them in a fixed order: results do not depend on timing).
+ * ggq_fused_batch_limit says up to which M this entry beats decoding the weight and calling a library GEMM. */
 int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, const void* x_bf16,
                  int32_t M, void* y, int32_t y_dtype, void* workspace,
                  size_t workspace_bytes, void* stream);

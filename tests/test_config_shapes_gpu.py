@@ -1,9 +1,10 @@
 """The public `matmul` on the benchmark configurations' own weight shapes and batches, sampled rows
 against the CPU oracle: the Llama-3.2-1B-shaped layer (Q4_K with attn_v / ffn_down in Q6_K) at batch
 1, 2, 4, 8, 16, and the Llama-3-8B-shaped Q5_K / Q6_K weights at batch 1, 32 and 128 through the
-router (above the small-batch cap it decodes on the device and calls the library GEMM) and through
-the fused tensor-core kernel by name.  Bar: relative L2 <= 2e-3 on the bf16 output and the
-reference's elementwise rtol = 1e-2, atol = 1e-2 max|ref|."""
+router (above its cap it decodes on the device and calls the library GEMM) and through the fused kernels by name.
+Bar: relative L2 <= 2e-3 on the bf16 output where the weights are not rounded (up to 32 rows), 4e-3 where they are
+rounded to bf16 first (the reference's contract for its GEMM and its fallback), and the reference's elementwise
+rtol = 1e-2, atol = 1e-2 max|ref|."""
 import numpy as np
 import pytest
 import torch
@@ -31,10 +32,11 @@ def check(product, name, qt, n, k, m):
     idx = torch.from_numpy(pick).cuda()
     ref = O.c_matmul(O.bf16_bits(x.float().cpu().numpy()), w.data[idx].cpu().numpy(), qt)
     got = y.float()[:, idx].cpu().numpy()
-    # above the router's cap `matmul` decodes the weight to bf16 (as the reference's fallback does) before the library
-    # GEMM, which adds the weights' own rounding: twice the bar of the fused route
-    fused = product is not gj.matmul or m <= gj.fused_batch_limit(w)
-    assert O.rel_l2(got, ref) <= (2e-3 if fused else 4e-3), (name, qt.name, n, k, m)
+    # up to 32 rows every fused kernel multiplies exact codes; above, both the fused tensor-core kernel and the fallback
+    # (decode to bf16 + library GEMM) round the weights to bf16 first, as the reference's own GEMM and fallback do:
+    # twice the bar
+    exact = m <= 32 and (product is not gj.matmul or m <= gj.fused_batch_limit(w))
+    assert O.rel_l2(got, ref) <= (2e-3 if exact else 4e-3), (name, qt.name, n, k, m)
     np.testing.assert_allclose(got, ref, rtol=1e-2, atol=1e-2 * np.abs(ref).max())
 
 

@@ -20,8 +20,9 @@ CODE_TYPES = [QT.Q4_K, QT.Q5_K, QT.Q6_K]
 
 @pytest.fixture(autouse=True)
 def _tcgen05_kernel_for_every_batch(monkeypatch):
-    # up to 128 rows ggq_gemm would otherwise hand these formats to the batch-major mma.sync kernel
-    monkeypatch.setenv("GGQ_WIDE_GEMM_MAX", "0")
+    # ggq_gemm would otherwise hand these formats to the batch-major mma.sync kernel (up to 32 rows) or to the
+    # bf16-weight tcgen05 kernel (above)
+    monkeypatch.setenv("GGQ_GEMM_KERNEL", "codes")
 
 
 def run(x, wb, qtype, out_dtype=torch.float32):

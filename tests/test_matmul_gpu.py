@@ -308,6 +308,13 @@ def test_q6k_batch1_kernel_activation_magnitudes(log2_scale):
 GEMM_TYPES = [QT.Q4_K, QT.Q5_K, QT.Q6_K, QT.IQ4_XS, QT.Q8_0, QT.IQ2_XS, QT.Q2_K]
 
 
+@pytest.fixture(autouse=True)
+def _tf32_kernel_for_the_gemm_tests(request, monkeypatch):
+    # Q4_K / Q5_K / Q6_K have faster kernels behind ggq_gemm; these tests are about the tf32 one that serves every format
+    if request.node.name.startswith("test_tensor_core_gemm"):
+        monkeypatch.setenv("GGQ_GEMM_KERNEL", "tf32")
+
+
 @pytest.mark.parametrize("qtype", GEMM_TYPES, ids=lambda t: t.name)
 @pytest.mark.parametrize("m", [17, 32, 100, 128, 200, 256, 300, 512])
 def test_tensor_core_gemm_matches_oracle(qtype, m):
@@ -316,10 +323,20 @@ def test_tensor_core_gemm_matches_oracle(qtype, m):
     x = synth.make_x(m, k, seed=m)
     ref = O.c_matmul(O.bf16_bits(x), w, qtype)
     got32 = run_fused(x, w, qtype, torch.float32)
-    # tf32 weights (11 significant bits, rounded to nearest): about 3e-4 relative L2; Q4_K and Q5_K take the
-    # integer-code kernel at this shape (rows 16-byte aligned), which is float32-exact
+    # tf32 weights (11 significant bits, rounded to nearest): about 3e-4 relative L2
     assert O.rel_l2(got32, ref) <= 1e-3, O.rel_l2(got32, ref)
     check_close(run_fused(x, w, qtype), ref)
+
+
+@pytest.mark.parametrize("m", [256 + 96, 512 + 88, 512 + 128, 768 + 240])
+def test_tensor_core_gemm_narrower_last_batch_tile(m):
+    # the last batch tile is narrower than the full ones, holds more stages and needs its own share of shared memory
+    # (Q8_0 and IQ4_XS always take the tf32 kernel; Q6_K takes it when its rows are not 16-byte aligned)
+    for qtype, n, k in [(QT.Q8_0, 200, 512), (QT.IQ4_XS, 130, 768), (QT.Q6_K, 128, 256)]:
+        w = synth.make_weight_bytes(n, k, qtype, seed=m)
+        x = synth.make_x(m, k, seed=m)
+        ref = O.c_matmul(O.bf16_bits(x), w, qtype)
+        assert O.rel_l2(run_fused(x, w, qtype, torch.float32), ref) <= 1e-3
 
 
 def test_tensor_core_gemm_large_tile_counts():

@@ -19,6 +19,12 @@ from oracle import oracle as O
 pytestmark = pytest.mark.gpu
 
 WIDE = [QT.Q4_K, QT.Q5_K, QT.Q6_K]
+
+
+@pytest.fixture(autouse=True)
+def _batch_major_kernel_for_every_batch(monkeypatch):
+    # above 32 rows ggq_gemm would otherwise pick the bf16-weight tcgen05 kernel
+    monkeypatch.setenv("GGQ_GEMM_KERNEL", "wide")
 BIG = (6144, 6144)            # 21 to 31 MB in these formats: above the size from which ggq_gemv picks this kernel
 
 
@@ -31,8 +37,8 @@ def to_x(x):
 
 
 def wide_direct(x, w, qt, n, k, out_dtype=torch.float32):
-    """ggq_gemm with the workspace: for these formats and up to 128 rows that is the batch-major kernel,
-    whatever the weight's size (ggq_gemv would pick it only for large weights)."""
+    """ggq_gemm with the workspace and the kernel pinned: the batch-major kernel in slices of 32 rows, whatever the
+    weight's size (ggq_gemv would pick it only for large weights)."""
     L = _lib.lib()
     m = x.shape[0]
     y = torch.empty((m, n), dtype=out_dtype, device="cuda")
@@ -126,7 +132,7 @@ def test_picked_by_the_small_batch_entry_for_large_weights(qtype):
     n, k = BIG
     wb = synth.make_weight_bytes(n, k, qtype, seed=5)
     w = on_device(wb, qtype, n, k)
-    assert gj.fused_batch_limit(w) == 32
+    assert gj.fused_batch_limit(w) >= 32
     for m in (5, 16):
         xb = synth.make_x(m, k, seed=m)
         ref = O.c_matmul(O.bf16_bits(xb), wb, qtype)
