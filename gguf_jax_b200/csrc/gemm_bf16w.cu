@@ -1,6 +1,6 @@
 // Fused decode + GEMM for batches from a few dozen to thousands of rows on the 5th-generation tensor cores
-// (tcgen05 / TMEM): Q4_K, Q5_K and Q6_K weights are decoded to float32 exactly as the decode kernel does,
-// rounded once to bf16 and written straight into the K-major, 128-byte-swizzled A tile in shared memory;
+// (tcgen05 / TMEM): Q4_K, Q5_K and Q6_K weights are decoded to float32 (Q6_K exactly as the decode kernel does;
+// Q4_K / Q5_K to within 2^-20 of a weight, see decode4), rounded once to bf16 and written straight into the K-major, 128-byte-swizzled A tile in shared memory;
 // the activations are used as they are (bf16, K-major: the B tile is a copy of 64 consecutive elements per
 // batch row); tcgen05.mma.kind::f16 accumulates the whole K range of the CTA in TMEM in float32.
 //
@@ -13,11 +13,12 @@
 //
 // A CTA owns 128 weight rows x MT batch columns (MT = 32, 64, 128 or 256 = the MMA N) and a range of K:
 //   producers (16 warps)  raw block bytes of the 128 rows arrive through a ring of whole superblocks
-//                         (cp.async, two superblocks ahead); per stage of 64 weights a thread decodes 16
-//                         weights of one row (byte -> float by a permute and one subtraction, one FMA with
-//                         the group's float32 scale and offset, packed conversion to bf16) and stores two
-//                         16-byte chunks of the A tile; the B tile's chunks are loaded one stage ahead into
-//                         registers and stored next to it;
+//                         (cp.async, two superblocks ahead); per superblock a thread unpacks the float32 scale and
+//                         offset of its groups once; per stage of 64 weights it decodes 16 weights of one row (one
+//                         byte permute and one FMA per weight, packed conversion to bf16) and stores two 16-byte
+//                         chunks of the A tile; with an even number of stages two stages are filled per round;
+//   loaders (4 warps)     copy the stage's 64 activations of every batch row of the tile straight from x into the
+//                         swizzled B tile (cp.async, 16 bytes), two stages ahead of announcing them;
 //   MMA warp (1 thread)   per stage four tcgen05.mma (K = 16 each) into the same TMEM accumulator,
 //                         tcgen05.commit frees the stage;
 //   epilogue              the producer warps, once their last stage is written: tcgen05.ld -> y, or, when K
@@ -122,10 +123,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&p);
 }
-// four code bytes -> four weights a * code + b -> two words of bf16 pairs
-__device__ __forceinline__ void decode4(uint32_t codes, float a, float b, uint32_t& lo, uint32_t& hi) {
-  lo = pack_bf16(fmaf(a, byte_to_float<0>(codes), b), fmaf(a, byte_to_float<1>(codes), b));
-  hi = pack_bf16(fmaf(a, byte_to_float<2>(codes), b), fmaf(a, byte_to_float<3>(codes), b));
+// byte SEL of v plus 128 as a float, exact, in one instruction: the bits 0x43vv0000 are 128 + v for v < 128
+template <int SEL>
+__device__ __forceinline__ float byte_plus_128(uint32_t v) {
+  return __uint_as_float(__byte_perm(v, 0x43000000u, 0x7044 + (SEL << 8)));
+}
+// four code bytes (each < 128) -> four weights a * code + b -> two words of bf16 pairs.  One permute and one FMA per
+// weight: a * (128 + code) + c with c = b - 128 a.  The FMA rounds once; c is exact for Q6_K (b = -32 a) and carries
+// one float32 rounding of about |a| 2^-17 for Q4_K / Q5_K, i.e. 2^-20 of a typical weight, before the bf16 rounding.
+__device__ __forceinline__ void decode4(uint32_t codes, float a, float c, uint32_t& lo, uint32_t& hi) {
+  lo = pack_bf16(fmaf(a, byte_plus_128<0>(codes), c), fmaf(a, byte_plus_128<1>(codes), c));
+  hi = pack_bf16(fmaf(a, byte_plus_128<2>(codes), c), fmaf(a, byte_plus_128<3>(codes), c));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -147,7 +155,7 @@ __device__ __forceinline__ float byte_of(uint32_t lo, uint32_t hi, int which) { 
 struct FQ4K {
   static constexpr int kQt = QT_Q4_K, kTs = 144, kRawPitch = 176;
   static constexpr bool kSplitChunks = false;
-  struct Prep { float a[4], b[4]; };          // group 2 s + h of stage s, h = qd / 2
+  struct Prep { float a[4], b[4]; };          // group 2 s + h of stage s, h = qd / 2: weight = a * (128 + code) + b
   __device__ static Prep prep(uint32_t blk, int qd) {
     const uint4 hd = lds_v4(blk);              // d | dmin, scales[0..3], scales[4..7], scales[8..11]
     const int h = qd >> 1;
@@ -165,6 +173,8 @@ struct FQ4K {
     p.b[1] = __fmul_rn(nd, h ? byte_to_float<3>(mn_lo) : byte_to_float<2>(mn_lo));
     p.b[2] = __fmul_rn(nd, h ? byte_to_float<1>(mn_hi) : byte_to_float<0>(mn_hi));
     p.b[3] = __fmul_rn(nd, h ? byte_to_float<3>(mn_hi) : byte_to_float<2>(mn_hi));
+#pragma unroll
+    for (int i = 0; i < 4; i++) p.b[i] = fmaf(-128.0f, p.a[i], p.b[i]);     // the offset decode4 wants
     return p;
   }
   template <int S>
@@ -245,7 +255,7 @@ struct FQ6K {
     load_words<2>(blk + 64 * n + 32 + 8 * qd, q1);
     load_words<2>(blk + 128 + 32 * n + 8 * qd, qh);
     const float a0 = p.a[2 * S], a1 = p.a[2 * S + 1];
-    const float b0 = -32.0f * a0, b1 = -32.0f * a1;
+    const float b0 = -160.0f * a0, b1 = -160.0f * a1;           // a * (128 + q) - 160 a = a * (q - 32), rounded once
 #pragma unroll
     for (int i = 0; i < 2; i++) {
       const uint32_t c0 = ((q0[i] >> nib) & 0x0F0F0F0Fu) | (((qh[i] >> hs) & 0x03030303u) << 4);
@@ -417,22 +427,46 @@ gemm_bf16w_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat
       const int blk = blk_begin + b;
       const uint32_t braw = raw_base + (b % kRawStages) * kRawBytes + t_row * F::kRawPitch + (uint32_t)(((int64_t)blk * F::kTs) & 15);
       const typename F::Prep pr = F::prep(braw, qd);
+      if constexpr (kStages % 2 == 0) {
+        // two stages per round: two independent decode chains per thread, half as many fences, waits and arrivals
+        // (a superblock starts at an even stage slot: the ring has an even number of slots and a superblock four stages)
 #pragma unroll
-      for (int sq = 0; sq < 4; sq++) {
-        if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, status)) { alive = false; break; }
-        const uint32_t stage = smem_base + s * kStageBytes;
-        uint32_t o[8];
-        if (sq == 0) F::template decode16<0>(braw, pr, qd, o);
-        else if (sq == 1) F::template decode16<1>(braw, pr, qd, o);
-        else if (sq == 2) F::template decode16<2>(braw, pr, qd, o);
-        else F::template decode16<3>(braw, pr, qd, o);
-        sts_v4(stage + a_dst0, o[0], o[1], o[2], o[3]);
-        sts_v4(stage + a_dst1, o[4], o[5], o[6], o[7]);
-        // make the generic-proxy stores visible to the tensor core, then one arrival per warp
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full_bar(s));
-        if (++s == kStages) { s = 0; ++round; }
+        for (int sq = 0; sq < 4; sq += 2) {
+          if (round > 0 && !(mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, status) &&
+                             mbar_wait(empty_bar(s + 1), (round - 1) & 1, abort_flag, status))) { alive = false; break; }
+          const uint32_t stage = smem_base + s * kStageBytes;
+          uint32_t o[8], o2[8];
+          if (sq == 0) { F::template decode16<0>(braw, pr, qd, o); F::template decode16<1>(braw, pr, qd, o2); }
+          else { F::template decode16<2>(braw, pr, qd, o); F::template decode16<3>(braw, pr, qd, o2); }
+          sts_v4(stage + a_dst0, o[0], o[1], o[2], o[3]);
+          sts_v4(stage + a_dst1, o[4], o[5], o[6], o[7]);
+          sts_v4(stage + kStageBytes + a_dst0, o2[0], o2[1], o2[2], o2[3]);
+          sts_v4(stage + kStageBytes + a_dst1, o2[4], o2[5], o2[6], o2[7]);
+          // make the generic-proxy stores visible to the tensor core, then one arrival per warp and stage
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(full_bar(s)); mbar_arrive(full_bar(s + 1)); }
+          s += 2;
+          if (s == kStages) { s = 0; ++round; }
+        }
+      } else {
+#pragma unroll
+        for (int sq = 0; sq < 4; sq++) {
+          if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, status)) { alive = false; break; }
+          const uint32_t stage = smem_base + s * kStageBytes;
+          uint32_t o[8];
+          if (sq == 0) F::template decode16<0>(braw, pr, qd, o);
+          else if (sq == 1) F::template decode16<1>(braw, pr, qd, o);
+          else if (sq == 2) F::template decode16<2>(braw, pr, qd, o);
+          else F::template decode16<3>(braw, pr, qd, o);
+          sts_v4(stage + a_dst0, o[0], o[1], o[2], o[3]);
+          sts_v4(stage + a_dst1, o[4], o[5], o[6], o[7]);
+          // make the generic-proxy stores visible to the tensor core, then one arrival per warp
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full_bar(s));
+          if (++s == kStages) { s = 0; ++round; }
+        }
       }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
