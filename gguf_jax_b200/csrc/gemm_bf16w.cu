@@ -11,7 +11,8 @@
 // 2e-3 on random data.  The small-batch kernels of this library (exact integer codes, float32 scales) do
 // not round the weights at all; this kernel trades that for tensor-core throughput.
 //
-// A CTA owns 128 weight rows x MT batch columns (MT = 32, 64, 128 or 256 = the MMA N) and a range of K:
+// A CTA owns 128 weight rows x MT batch columns (MT = 32 .. 256 = the MMA N, or 512 as two MMAs of 256 columns into
+// the two halves of the 512-column tensor memory) and a range of K:
 //   producers (16 warps)  raw block bytes of the 128 rows arrive through a ring of whole superblocks
 //                         (cp.async, two superblocks ahead); per superblock a thread unpacks the float32 scale and
 //                         offset of its groups once; per stage of 64 weights it decodes 16 weights of one row (one
@@ -28,8 +29,12 @@
 // ggq_read_status), the CTA falls through to the common exit and TMEM is always released.
 #include "gemv.cuh"
 
+#include <cuda.h>
+
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
+#include <cstring>
 
 namespace ggq {
 namespace gemmb {
@@ -266,7 +271,7 @@ struct FQ6K {
   }
 };
 
-template <int MT> constexpr int stages_of() { return MT >= 256 ? 3 : 4; }
+template <int MT> constexpr int stages_of() { return MT >= 512 ? 2 : MT >= 256 ? 3 : 4; }
 template <class F, int MT> constexpr int raw_stages_of() {
   return (stages_of<MT>() * (kABytes + MT * 128) + 3 * kTileN * F::kRawPitch + 2304 <= kSmemLimit) ? 3 : 2;
 }
@@ -278,7 +283,7 @@ template <class F, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16w_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat16* __restrict__ x, int M,
                   void* __restrict__ y, int y_dtype, int* __restrict__ status, float* __restrict__ partials,
-                  int* __restrict__ counters) {
+                  int* __restrict__ counters, const __grid_constant__ CUtensorMap x_map, const int use_tma) {
   constexpr int kStages = stages_of<MT>(), kRawStages = raw_stages_of<F, MT>();
   constexpr int kBBytes = MT * 128, kStageBytes = kABytes + kBBytes, kRawBytes = kTileN * F::kRawPitch;
   extern __shared__ uint8_t smem_raw[];
@@ -306,15 +311,15 @@ gemm_bf16w_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat
 
   if (tid == 0) {
     for (int s = 0; s < kStages; s++) {
-      mbar_init(full_bar(s), kProducerWarps + kLoaderWarps);
+      mbar_init(full_bar(s), kProducerWarps + (use_tma ? 1 : kLoaderWarps));   // + the B tile's announcement(s)
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(acc_bar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (m0 + MT > M) {
-    // batch rows past the end are never copied: their B rows stay zero
+  if (!use_tma && m0 + MT > M) {
+    // batch rows past the end are never copied: their B rows stay zero (the tensor-map copy fills them itself)
     for (int i = tid; i < kStages * (kBBytes / 16); i += kThreads) {
       const int st = i / (kBBytes / 16), q = i % (kBBytes / 16);
       sts_v4(smem_base + st * kStageBytes + kABytes + 16 * q, 0u, 0u, 0u, 0u);
@@ -322,7 +327,7 @@ gemm_bf16w_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   const int mma_warp = kProducerWarps;
-  constexpr uint32_t kTmemCols = MT < 32 ? 32 : MT;
+  constexpr uint32_t kTmemCols = MT < 32 ? 32 : MT;      // 32 .. 512: a power of two
   if (warp == mma_warp) {   // the MMA warp owns the TMEM allocation
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
@@ -335,7 +340,8 @@ gemm_bf16w_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat
 
   if (warp == mma_warp) {
     // ------------------------------- MMA issue -------------------------------
-    const uint32_t idesc = umma_idesc(kTileN, MT);
+    constexpr int kMmaN = MT > 256 ? 256 : MT;       // 512 columns are two MMAs per step into the two halves of the accumulator
+    const uint32_t idesc = umma_idesc(kTileN, kMmaN);
     bool ok = true;
     for (int st = 0; st < n_stages && ok; st++) {
       const int s = st % kStages, it = st / kStages;
@@ -345,8 +351,12 @@ gemm_bf16w_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat
       if (lane == 0) {
         const uint32_t a_addr = smem_base + s * kStageBytes, b_addr = a_addr + kABytes;
 #pragma unroll
-        for (int kk = 0; kk < kStageK / 16; kk++)
-          umma_bf16(tmem_base, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), idesc, (st > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < kStageK / 16; kk++) {
+#pragma unroll
+          for (int half = 0; half < MT / kMmaN; half++)
+            umma_bf16(tmem_base + half * kMmaN, umma_desc(a_addr + kk * 32), umma_desc(b_addr + half * (kMmaN * 128) + kk * 32), idesc,
+                      (st > 0 || kk > 0) ? 1u : 0u);
+        }
         umma_commit(empty_bar(s));                  // the stage may be refilled once these MMAs have read it
         if (st == n_stages - 1) umma_commit(acc_bar);   // and the accumulator is complete
       }
@@ -358,6 +368,27 @@ gemm_bf16w_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat
     // arrival for a stage follows one stage later, after its copies have landed and a proxy fence (cp.async writes through
     // the generic proxy, the tensor core reads through the async proxy).
     const int ltid = (warp - mma_warp - 1) * 32 + lane;
+    if (use_tma) {
+      // One thread, one instruction per stage: a 64-element x MT-row box of x (bf16, row-major [M, K]) lands in the
+      // 128-byte-swizzled B tile; rows past M are zero-filled by the copy; completion is counted in bytes on the
+      // stage's "full" barrier.  The other loader lanes have nothing to do.
+      if (ltid == 0) {
+        bool ok = true;
+        for (int st = 0; st < n_stages && ok; st++) {
+          const int s = st % kStages, it = st / kStages;
+          if (it > 0) ok = mbar_wait(empty_bar(s), (it - 1) & 1, abort_flag, status);
+          if (!ok) break;
+          const uint32_t bt = smem_base + s * kStageBytes + kABytes, bar = full_bar(s);
+          const int k0 = (blk_begin * 4 + st) * kStageK;
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)kBBytes) : "memory");
+          constexpr int kBoxRows = MT > 256 ? 256 : MT;      // a box has at most 256 rows
+#pragma unroll
+          for (int half = 0; half < MT / kBoxRows; half++)
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                         ::"r"(bt + half * (kBoxRows * 128)), "l"(&x_map), "r"(k0), "r"(m0 + half * kBoxRows), "r"(bar) : "memory");
+        }
+      }
+    } else {
     constexpr int kL = 32 * kLoaderWarps, kPer = (MT * 8 + kL - 1) / kL;      // chunks per loader thread and stage
     // chunk q = ltid + i * kL: batch row q / 8, 16-byte piece q % 8; consecutive i are kL / 8 rows apart, i.e. a whole
     // number of 8-row swizzle groups, so both addresses advance by constants
@@ -393,6 +424,7 @@ gemm_bf16w_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    }
   } else {
     // ------------------------------- producers -------------------------------
     const int ptid = tid;                                            // 0..511
@@ -427,7 +459,7 @@ gemm_bf16w_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat
       const int blk = blk_begin + b;
       const uint32_t braw = raw_base + (b % kRawStages) * kRawBytes + t_row * F::kRawPitch + (uint32_t)(((int64_t)blk * F::kTs) & 15);
       const typename F::Prep pr = F::prep(braw, qd);
-      if constexpr (kStages % 2 == 0) {
+      if constexpr (kStages % 2 == 0 && kStages >= 4) {
         // two stages per round: two independent decode chains per thread, half as many fences, waits and arrivals
         // (a superblock starts at an even stage slot: the ring has an even number of slots and a superblock four stages)
 #pragma unroll
@@ -515,19 +547,24 @@ gemm_bf16w_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat
       if (*last_flag && out_row < N) {
         __threadfence();
         const int64_t zs = (int64_t)M * N;                          // stride between the ranges' partial tiles
-        for (int c = 0; c < kColsPerWarp; c++) {
-          const int m = m0 + cpart * kColsPerWarp + c;
-          if (m < M) {
-            const float* p = partials + (int64_t)m * N + out_row;
-            float sum = 0.f;
-            int z = 0;
-            for (; z + 4 <= splits; z += 4) {                       // four loads in flight, added in range order
-              const float v0 = __ldcg(p + z * zs), v1 = __ldcg(p + (z + 1) * zs), v2 = __ldcg(p + (z + 2) * zs), v3 = __ldcg(p + (z + 3) * zs);
-              sum = ((sum + v0) + v1) + v2 + v3;
+        // four batch columns at a time, the ranges in order: 4 independent chains keep 4 loads in flight per thread
+        for (int c = 0; c < kColsPerWarp; c += 4) {
+          const int mb = m0 + cpart * kColsPerWarp + c;
+          const float* p = partials + (int64_t)mb * N + out_row;
+          float sum[4] = {0.f, 0.f, 0.f, 0.f};
+          // columns past M read column mb again (never stored): no branches around the loads
+          const int64_t o1 = mb + 1 < M ? N : 0, o2 = mb + 2 < M ? 2 * (int64_t)N : 0, o3 = mb + 3 < M ? 3 * (int64_t)N : 0;
+          if (mb < M) {
+#pragma unroll 4
+            for (int z = 0; z < splits; z++) {
+              const float* q = p + z * zs;
+              const float v0 = __ldcg(q), v1 = __ldcg(q + o1), v2 = __ldcg(q + o2), v3 = __ldcg(q + o3);
+              sum[0] += v0; sum[1] += v1; sum[2] += v2; sum[3] += v3;
             }
-            for (; z < splits; z++) sum += __ldcg(p + z * zs);
-            store_out(y, y_dtype, (int64_t)m * N + out_row, sum);
           }
+#pragma unroll
+          for (int i = 0; i < 4; i++)
+            if (mb + i < M) store_out(y, y_dtype, (int64_t)(mb + i) * N + out_row, sum[i]);
         }
       }
     }
@@ -540,7 +577,39 @@ gemm_bf16w_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat
   }
 }
 
-static int tile_m_of(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+static int tile_m_of(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : M <= 256 ? 256 : 512; }
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against the driver library).
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static std::atomic<void*> cached{nullptr};
+  static std::atomic<bool> tried{false};
+  if (!tried.load(std::memory_order_acquire)) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    (void)cudaGetLastError();
+    cached.store(fn, std::memory_order_release);
+    tried.store(true, std::memory_order_release);
+  }
+  return reinterpret_cast<EncodeTiledFn>(cached.load(std::memory_order_acquire));
+}
+// Tensor map of x as bf16 [M rows, K columns], box = 64 columns x box_rows rows, 128-byte swizzle, zero fill outside.
+static bool make_x_map(CUtensorMap* map, const void* x, int64_t M, int64_t K, int box_rows) {
+  static const bool off = [] { const char* e = getenv("GGQ_GEMM_NO_TMA"); return e && e[0] == '1'; }();
+  EncodeTiledFn fn = off ? nullptr : encode_tiled_fn();
+  if (!fn || (uintptr_t)x % 16 || (K * 2) % 16) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kStageK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 template <class F, int MT>
 static cudaError_t launch_mt(const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y, int y_dtype, int* status,
@@ -556,20 +625,26 @@ static cudaError_t launch_mt(const uint8_t* w, int64_t N, int64_t K, const void*
   }
   float* partials = reinterpret_cast<float*>(ws + kWsGemmPartialOffset);
   int* counters = reinterpret_cast<int*>(ws + kWsCounterOffset);
+  // the B tile comes by TMA when the driver offers the tensor-map encoder (it does from CUDA 12.0 on); otherwise the
+  // loader warps copy it with cp.async
+  alignas(64) CUtensorMap x_map;
+  memset(&x_map, 0, sizeof(x_map));
+  const int use_tma = make_x_map(&x_map, x, M, K, MT > 256 ? 256 : MT) ? 1 : 0;
   dim3 grid((unsigned)((N + kTileN - 1) / kTileN), (unsigned)((M + MT - 1) / MT), (unsigned)splits);
   gemm_bf16w_kernel<F, MT><<<grid, kThreads, smem_bytes<F, MT>(), st>>>(w, (int)N, (int)K, (const __nv_bfloat16*)x, M, y, y_dtype,
-                                                                        status, partials, counters);
+                                                                        status, partials, counters, x_map, use_tma);
   return cudaPeekAtLastError();
 }
 
 template <class F>
 static cudaError_t launch(const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y, int y_dtype, int* status,
-                          int splits, uint8_t* ws, cudaStream_t st) {
-  switch (tile_m_of(M)) {
+                          int mt, int splits, uint8_t* ws, cudaStream_t st) {
+  switch (mt) {
     case 32: return launch_mt<F, 32>(w, N, K, x, M, y, y_dtype, status, splits, ws, st);
     case 64: return launch_mt<F, 64>(w, N, K, x, M, y, y_dtype, status, splits, ws, st);
     case 128: return launch_mt<F, 128>(w, N, K, x, M, y, y_dtype, status, splits, ws, st);
-    default: return launch_mt<F, 256>(w, N, K, x, M, y, y_dtype, status, splits, ws, st);
+    case 256: return launch_mt<F, 256>(w, N, K, x, M, y, y_dtype, status, splits, ws, st);
+    default: return launch_mt<F, 512>(w, N, K, x, M, y, y_dtype, status, splits, ws, st);
   }
 }
 
@@ -582,23 +657,32 @@ bool gemm_bf16w_applicable(int qtype, int64_t N, int64_t K, int M) {
          (int64_t)M * N < (1ll << 40);
 }
 
-// How many K ranges a launch uses: the count that minimises (waves of CTAs) / (ranges), with a small charge per
-// range for the partial tiles.  One CTA is resident per SM.
-int gemm_bf16w_splits(int64_t N, int64_t K, int M, int sm_count) {
+// Batch tile and number of K ranges of a launch: the pair that minimises
+//   waves of CTAs x (superblocks of a CTA x time per superblock + 4 us to start and drain a CTA) + the partial tiles' round trip,
+// with the time per superblock (2.3 us + 3.5 ns per batch column) and the other constants fitted to B200 timings.
+// One CTA is resident per SM.  Above 256 rows the choice is between one 512-column tile (the weights are decoded once,
+// fewer CTAs) and 256-column tiles (twice the decoding, twice the CTAs: better for few row tiles).
+static void choose_tiling(int64_t N, int64_t K, int M, int sm_count, int* mt_out, int* splits_out) {
   if (sm_count <= 0) sm_count = 148;
-  const int mt = gemmb::tile_m_of(M);
-  const int64_t tiles = ((N + gemmb::kTileN - 1) / gemmb::kTileN) * ((M + mt - 1) / mt);
   const int64_t SB = K / 256;
-  int best = 1;
+  const int mt_lo = gemmb::tile_m_of(M > 256 ? 256 : M), mt_hi = gemmb::tile_m_of(M);
   double best_cost = 1e30;
-  for (int s = 1; s <= gemmb::kMaxSplits && s <= SB; s++) {
-    const double waves = (double)((tiles * s + sm_count - 1) / sm_count);
-    // time ~ waves x (superblocks of a CTA at about 2.5 us each + 4 us to start and drain a CTA) + writing and
-    // re-reading the partial tiles
-    const double cost = waves * ((double)((SB + s - 1) / s) * 2.5 + 4.0) + (s > 1 ? 2.0 + 0.004 * s * mt : 0.0);
-    if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+  for (int mt = mt_lo; mt <= mt_hi; mt *= 2) {
+    const int64_t tiles = ((N + gemmb::kTileN - 1) / gemmb::kTileN) * ((M + mt - 1) / mt);
+    const double t_sb = 2.3 + 0.0035 * mt;
+    // a 512-column tile is cut into at most two K ranges: its partial tiles are 256 KB each, and four or more of them
+    // per row tile were measured far slower than the model says (4096 x 14336 at 512 rows: 205 us against 120 us)
+    for (int s = 1; s <= (mt > 256 ? 2 : gemmb::kMaxSplits) && s <= SB; s++) {
+      const double waves = (double)((tiles * s + sm_count - 1) / sm_count);
+      const double cost = waves * ((double)((SB + s - 1) / s) * t_sb + 4.0) + (s > 1 ? 2.0 + 0.02 * s * mt : 0.0);
+      if (cost < best_cost - 1e-9) { best_cost = cost; *mt_out = mt; *splits_out = s; }
+    }
   }
-  return best;
+}
+int gemm_bf16w_splits(int64_t N, int64_t K, int M, int sm_count) {
+  int mt = 32, s = 1;
+  choose_tiling(N, K, M, sm_count, &mt, &s);
+  return s;
 }
 
 // Scratch: arrival counters in the counter area every kernel shares; partial tiles (splits x M x N float32) when K is split.
@@ -613,15 +697,15 @@ size_t gemm_bf16w_workspace_bytes(int qtype, int64_t N, int64_t K, int M, int sm
 cudaError_t gemm_bf16w(int qtype, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y, int y_dtype,
                        int* status, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st) {
   if (!ws || (uintptr_t)ws % 256 || ws_bytes < gemm_bf16w_workspace_bytes(qtype, N, K, M, sm_count)) return cudaErrorInvalidValue;
-  const int splits = gemm_bf16w_splits(N, K, M, sm_count);
-  const int mt = gemmb::tile_m_of(M);
+  int mt = 32, splits = 1;
+  choose_tiling(N, K, M, sm_count, &mt, &splits);
   const int64_t tiles = ((N + gemmb::kTileN - 1) / gemmb::kTileN) * ((M + mt - 1) / mt);
   if (kWsCounterOffset + (size_t)tiles * sizeof(int) > kWsGemmPartialOffset) return cudaErrorInvalidValue;
   uint8_t* base = reinterpret_cast<uint8_t*>(ws);
   switch (qtype) {
-    case QT_Q4_K: return gemmb::launch<gemmb::FQ4K>(w, N, K, x, M, y, y_dtype, status, splits, base, st);
-    case QT_Q5_K: return gemmb::launch<gemmb::FQ5K>(w, N, K, x, M, y, y_dtype, status, splits, base, st);
-    case QT_Q6_K: return gemmb::launch<gemmb::FQ6K>(w, N, K, x, M, y, y_dtype, status, splits, base, st);
+    case QT_Q4_K: return gemmb::launch<gemmb::FQ4K>(w, N, K, x, M, y, y_dtype, status, mt, splits, base, st);
+    case QT_Q5_K: return gemmb::launch<gemmb::FQ5K>(w, N, K, x, M, y, y_dtype, status, mt, splits, base, st);
+    case QT_Q6_K: return gemmb::launch<gemmb::FQ6K>(w, N, K, x, M, y, y_dtype, status, mt, splits, base, st);
     default: return cudaErrorInvalidValue;
   }
 }

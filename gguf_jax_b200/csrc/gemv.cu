@@ -33,10 +33,11 @@ inline bool wide_pays(int qtype, int64_t weight_bytes) {
 // batch measured and are reached only by name, above 128 rows or for the other formats.
 constexpr int kWideRouterBatch = 32;
 // Above 32 rows the bf16-weight tcgen05 kernel (gemm_bf16w.cu; the fallback's own precision) is compared with the same
-// fallback: on the large weights it wins up to 256 rows (Q6_K 14336 x 4096: 55 / 60 / 72 us at 64 / 128 / 256 rows against
-// 67 / 68 / 75 us; Q4_K: 42 / 45 / 60 us) and loses from 512 on, where the activations' tile no longer fits one CTA
-// and the weights are decoded once per 256 rows (142 us against 92 us); on weights of a few MB the fallback's library
-// GEMM reads a decoded copy that stays in the L2 and wins from 64 rows on.
+// fallback: on the large weights it wins up to 256 rows (Q6_K 14336 x 4096: 52 / 55 / 62 us at 64 / 128 / 256 rows against
+// 67 / 68 / 75 us; Q6_K 4096 x 14336: 54 / 62 / 79 us against 70 / 73 / 80 us), and up to 512 rows where there are enough
+// row tiles to fill the device without cutting K (14336 rows: 78 us against 92 us; 4096 rows: 118 us against 92 us);
+// on weights of a few MB the fallback's library GEMM reads a decoded copy that stays in the L2 and wins from 64 rows on.
+constexpr int kGemmRouterBatchWide = 512;      // at least 96 row tiles of 128 rows
 constexpr int kGemmRouterBatch = 256;
 }
 
@@ -47,7 +48,7 @@ extern "C" int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K) {
   if (!ti || !ti->fused || N <= 0 || K <= 0 || K % ti->block_elems) return 0;
   if (is_k_quant(qtype) && K % 256 == 0 && (K / 256 * ti->block_bytes) % 16 == 0 &&
       wide_pays(qtype, N * (K / 256) * (int64_t)ti->block_bytes) && gemv_wide_applicable(qtype, N, K, kWideRouterBatch, nullptr, nullptr))
-    return gemm_bf16w_applicable(qtype, N, K, kGemmRouterBatch) ? kGemmRouterBatch : kWideRouterBatch;
+    return !gemm_bf16w_applicable(qtype, N, K, kGemmRouterBatch) ? kWideRouterBatch : N >= 96 * 128 ? kGemmRouterBatchWide : kGemmRouterBatch;
   return kGemvMaxBatch;
 }
 
