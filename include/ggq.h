@@ -86,7 +86,7 @@ int32_t ggq_dequant(int32_t qtype, const void* blocks, int64_t n_blocks, void* o
 int32_t ggq_has_fused(int32_t qtype);
 
 /* Largest flattened batch M for which the fused route (ggq_gemv up to ggq_gemv_max_batch(), ggq_gemm above) is
- * the faster one for an (N, K) weight of qtype -- 16, or 256 for Q4_K / Q5_K / Q6_K weights of tens of MB; 0 when
+ * the faster one for an (N, K) weight of qtype -- 16, or 256 / 512 for Q4_K / Q5_K / Q6_K weights of tens of MB; 0 when
  * there is no fused kernel.  Replaces the per-kernel caps
  * (src/gguf_jax/_matmul.py:60-75, cute/q4_k.py:117-118, cute/lowbit.py:97). */
 int32_t ggq_fused_batch_limit(int32_t qtype, int64_t N, int64_t K);

@@ -93,7 +93,7 @@ def test_router_takes_it_up_to_its_cap_on_large_weights(qtype, monkeypatch):
     n, k = 6144, 6144
     w = synth.make_weight_on_device(n, k, qtype, seed=5, device="cuda")
     cap = gj.fused_batch_limit(w)
-    assert cap == 256
+    assert cap == 256            # 48 row tiles: large, but not enough tiles for the 512-row cap
     pick = np.sort(np.random.default_rng(0).choice(n, size=64, replace=False))
     idx = torch.from_numpy(pick).cuda()
     rows = w.data[idx].cpu().numpy()
