@@ -191,8 +191,8 @@ def decode_leg(world: int, rank: int, dev, batch: int = 1, route: str = "fused")
     lm_head reads the last down output.  (Attention, norms and activations are not run, so the
     numbers mean nothing; the block scales are shifted by powers of two beforehand so that the
     magnitudes stay near one along the chain.)  On N > 1 ranks every product is row-sharded and
-    its result reaches every rank through the tagged exchange inside the kernels (batch 1) or an
-    NCCL all-gather after the kernel (larger batches: the in-kernel exchanges are batch-1 paths).
+    its result reaches every rank through an exchange inside the kernels: tagged words at batch 1,
+    peer stores plus one flag per launch for larger batches.
     `route` "fused" calls the fused kernels by name (above the small-batch cap that is the tcgen05
     code GEMM); "router" calls `matmul`, which above the cap decodes and calls the library GEMM."""
     import torch
@@ -220,10 +220,22 @@ def decode_leg(world: int, rank: int, dev, batch: int = 1, route: str = "fused")
     x0 = torch.from_numpy(synth.make_x(batch, 8192, seed=8192)).to(dev).to(torch.bfloat16)
     product = kernels.fused_matmul if route == "fused" else gj.matmul
 
-    if batch > 1:
+    if batch > 1 and world > 1:
+        # the batch-major kernel stores this rank's columns of every batch row into every rank's buffer and raises a flag
+        # (ggq_gemm_sharded); a product may read the leading columns of a buffer two launches back, hence four buffers
+        po = sharded.PeerOutput(None, max_batch=batch, n_total=DECODE_HEAD[2], device=dev, n_buffers=4)
+
         def mm(x, w):
-            return sharded.gather_columns(product(x[:, :w.shape[1]].contiguous(), w)) if world > 1 else \
-                product(x[:, :w.shape[1]].contiguous(), w)
+            return po.matmul(x[:, :w.shape[1]], w, wait_previous=True)
+
+        def value(h):
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            return h.clone()
+    elif batch > 1:
+        def mm(x, w):
+            return product(x[:, :w.shape[1]].contiguous(), w)
 
         def value(h):
             return h
@@ -373,7 +385,7 @@ def decode_leg(world: int, rank: int, dev, batch: int = 1, route: str = "fused")
     wbytes += DECODE_HEAD[2] * (DECODE_HEAD[3] // 256) * _BLOCK_BYTES[DECODE_HEAD[1]]
     del graph
     exchange = "none" if world == 1 else (
-        "NCCL all-gather after each kernel" if batch > 1 else
+        "stored into every rank's buffer by the batch-major kernel, one flag per launch (ggq_gemm_sharded)" if batch > 1 else
         "tagged words stored into every rank's buffer by the kernels (ggq_gemv_sharded_tagged)")
     return {"tok_s": batch * 1e3 / ms, "ms_per_token": ms / batch, "ms_per_step": ms, "batch": batch, "route": route, "launches_per_step": launches,
             "weight_gb_per_step": wbytes / 1e9, "aggregate_hbm_gbs": wbytes / (ms * 1e-3) / 1e9,

@@ -47,6 +47,11 @@ SIGNATURES = {
                                           ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int32,
                                           ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
                                           ctypes.c_size_t, ctypes.c_void_p]),
+    "ggq_gemm_sharded": (ctypes.c_int32, [ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                          ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p),
+                                          ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int32,
+                                          ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                                          ctypes.c_size_t, ctypes.c_void_p]),
     "ggq_gemv_sharded_tagged": (ctypes.c_int32, [ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                                  ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
                                                  ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,

@@ -210,6 +210,56 @@ extern "C" int32_t ggq_gemv_sharded(int32_t qtype, const void* w, int64_t N_loca
   return GGQ_OK;
 }
 
+extern "C" int32_t ggq_gemm_sharded(int32_t qtype, const void* w, int64_t N_local, int64_t K, const void* x_bf16, int64_t ldx,
+                                    int32_t M, void* const* y_peers, uint32_t* const* flag_peers, int32_t world, int32_t rank,
+                                    int64_t n_total, int32_t y_dtype, int32_t wait_previous, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
+  if (M == 1)
+    return ggq_gemv_sharded(qtype, w, N_local, K, x_bf16, 1, y_peers, flag_peers, world, rank, n_total, y_dtype, wait_previous,
+                            workspace, workspace_bytes, stream);
+  const TypeInfo* ti = type_info(qtype);
+  if (!ti) return fail(GGQ_BAD_QTYPE, "ggq_gemm_sharded: qtype %d is not decodable", qtype);
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+    return fail(GGQ_BAD_SHAPE, "ggq_gemm_sharded: rank %d of %d (at most %d ranks)", rank, world, kMaxPeers);
+  if (M < 1 || N_local <= 0 || K <= 0 || K % ti->block_elems || n_total < (int64_t)world * N_local || ldx < K || (ldx * 2) % 16)
+    return fail(GGQ_BAD_SHAPE, "ggq_gemm_sharded: M=%d N_local=%lld K=%lld ldx=%lld n_total=%lld (ldx >= K, rows 16-byte aligned)", M,
+                (long long)N_local, (long long)K, (long long)ldx, (long long)n_total);
+  if (y_dtype != GGQ_F32 && y_dtype != GGQ_BF16 && y_dtype != GGQ_F16)
+    return fail(GGQ_BAD_DTYPE, "ggq_gemm_sharded: y_dtype %d", y_dtype);
+  if (!w || !x_bf16 || !y_peers || !flag_peers) return fail(GGQ_MISALIGNED, "ggq_gemm_sharded: null pointer");
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int slice = gemv_wide_max_batch();
+  const int first = M < slice ? M : slice;
+  if (!is_k_quant(qtype) || !gemv_wide_applicable(qtype, N_local, K, first, w, x_bf16))
+    return fail(GGQ_UNSUPPORTED, "ggq_gemm_sharded: only Q4_K / Q5_K / Q6_K weights with K a multiple of 256 and 16-byte aligned rows "
+                "publish batches to peers; use ggq_gemm plus an all-gather for qtype %d, K=%lld", qtype, (long long)K);
+  const size_t need = gemv_wide_workspace_bytes(qtype, N_local, K, first, sm_count_of(dev));
+  if (!workspace || workspace_bytes < need || (uintptr_t)workspace % 256)
+    return fail(GGQ_BAD_WORKSPACE, "ggq_gemm_sharded: workspace of %zu bytes needed", need);
+  const int y_item = y_dtype == GGQ_F32 ? 4 : 2;
+  // slices of up to 32 batch rows, one exchange each; only the first has to wait for the activations, and a consumer that waits
+  // for the last one has the earlier ones too (a rank raises its flags in launch order, each behind a system-scope fence)
+  for (int m0 = 0; m0 < M; m0 += slice) {
+    const int mb = M - m0 < slice ? M - m0 : slice;
+    PeerPublish pp = {};
+    for (int p = 0; p < world; p++) {
+      if (!y_peers[p] || !flag_peers[p]) return fail(GGQ_MISALIGNED, "ggq_gemm_sharded: null peer pointer %d", p);
+      pp.y[p] = (uint8_t*)y_peers[p] + (size_t)m0 * n_total * y_item;
+      pp.flags[p] = flag_peers[p];
+    }
+    pp.world = world;
+    pp.rank = rank;
+    pp.n_total = n_total;
+    pp.row_offset = (int64_t)rank * N_local;
+    pp.wait_previous = (wait_previous && m0 == 0) ? 1 : 0;
+    cudaError_t err = gemv_wide(qtype, (const uint8_t*)w, N_local, K, (const uint8_t*)x_bf16 + (size_t)m0 * ldx * 2, mb, nullptr, y_dtype,
+                                workspace, workspace_bytes, sm_count_of(dev), (cudaStream_t)stream, ldx, &pp, device_status_word(dev));
+    if (err != cudaSuccess) return fail(GGQ_LAUNCH_FAILED, "ggq_gemm_sharded: %s", cudaGetErrorString(err));
+  }
+  return GGQ_OK;
+}
+
 extern "C" int32_t ggq_gemv_sharded_tagged(int32_t qtype, const void* w, int64_t N_local, int64_t K,
                                            const void* x_bf16, const uint32_t* x_tagged, int32_t x_back,
                                            const uint32_t* after_tagged, int64_t after_words, int32_t after_back,

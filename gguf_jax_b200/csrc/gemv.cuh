@@ -262,8 +262,10 @@ cudaError_t gemm_bf16w(int qtype, const uint8_t* w, int64_t N, int64_t K, const 
 int gemv_wide_max_batch();
 bool gemv_wide_applicable(int qtype, int64_t N, int64_t K, int M, const void* w, const void* x);
 size_t gemv_wide_workspace_bytes(int qtype, int64_t N, int64_t K, int M, int sm_count);
+// ldx: elements between batch rows of x (0: K); peers: row-sharded output with the flag protocol (then y is ignored).
 cudaError_t gemv_wide(int qtype, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y, int y_dtype,
-                      void* ws, size_t ws_bytes, int sm_count, cudaStream_t st);
+                      void* ws, size_t ws_bytes, int sm_count, cudaStream_t st, int64_t ldx = 0,
+                      const PeerPublish* peers = nullptr, int* status = nullptr);
 
 // Medium batches of Q4_K / Q5_K / Q6_K: tcgen05 kernel with exact integer codes as bf16 operands and one
 // TMEM slot per scale group (gemm_codes.cu).

@@ -140,14 +140,18 @@ struct Geo {
 //   S_col[col]          the column's power-of-two exponent
 template <class F, int XR>
 __global__ void __launch_bounds__(256)
-prepare_kernel(const __nv_bfloat16* __restrict__ x, int K, int M, uint8_t* __restrict__ xp, uint8_t* __restrict__ xo, int* __restrict__ S_col) {
+prepare_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int K, int M, uint8_t* __restrict__ xp, uint8_t* __restrict__ xo,
+               int* __restrict__ S_col, const PeerPublish pp, int* __restrict__ status) {
   __shared__ int s_max;
   pdl_wait();            // x may be the previous kernel's output, and the previous launch may still read the staged copy
   pdl_trigger();         // the multiply kernel may start fetching weights
   const int col = blockIdx.x, tid = threadIdx.x;
+  // row-sharded: x is what the peers stored during the previous exchange; wait (bounded) for all of their flags
+  peer_wait_previous(pp, tid, status);
+  if (pp.world > 0 && pp.wait_previous) __syncthreads();
   const int SB = K / 256;
   const bool real = col < M;
-  const __nv_bfloat16* xr = x + (int64_t)(real ? col : 0) * K;
+  const __nv_bfloat16* xr = x + (int64_t)(real ? col : 0) * ldx;
   if (tid == 0) s_max = 0;
   __syncthreads();
   float amax = 0.f;
@@ -445,7 +449,7 @@ template <class F, int NT>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gemv_wide_kernel(const uint8_t* __restrict__ w, int N, int K, const uint8_t* __restrict__ xp, const uint8_t* __restrict__ xo,
                  const int* __restrict__ S_col, int M, void* __restrict__ y, int y_dtype, int* __restrict__ counters,
-                 float* __restrict__ slots, const Geo geo) {
+                 float* __restrict__ slots, const Geo geo, const PeerPublish pp) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_last;
   constexpr int XR = 8 * NT;
@@ -529,7 +533,14 @@ gemv_wide_kernel(const uint8_t* __restrict__ w, int N, int K, const uint8_t* __r
 #pragma unroll
       for (int i = 0; i < 4; i++) {
         const int row = rb * kBlockRows + warp * 16 + g + 8 * (i >> 1), col = nt * 8 + 2 * t + (i & 1);
-        if (row < N && col < M) store_out(y, y_dtype, (int64_t)col * N + row, v[nt][i] * unscale[nt][i & 1]);
+        if (row < N && col < M) {
+          const float val = v[nt][i] * unscale[nt][i & 1];
+          if (pp.world == 0) store_out(y, y_dtype, (int64_t)col * N + row, val);
+          else {            // row-sharded: this rank's rows of every rank's (M, n_total) output
+#pragma unroll 1
+            for (int p = 0; p < pp.world; p++) store_out(pp.y[p], y_dtype, (int64_t)col * pp.n_total + pp.row_offset + row, val);
+          }
+        }
       }
     }
   };
@@ -594,6 +605,7 @@ gemv_wide_kernel(const uint8_t* __restrict__ w, int N, int K, const uint8_t* __r
     if (++k == SB) { k = 0; ++rb; }
   }
   cp_async_wait_pending(0);
+  peer_publish(pp, tid, gridDim.x);        // row-sharded: raise this rank's flag on every rank once the whole grid has stored
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -642,8 +654,8 @@ static WsLayout ws_layout(const FormatInfo& fi, int64_t K, int M, int sm_count) 
 }
 
 template <class F, int NT>
-static cudaError_t launch(const Geo& geo, int grid, cudaStream_t st, const uint8_t* w, int N, int K, const void* x, int M,
-                          void* y, int y_dtype, uint8_t* ws, const WsLayout& l) {
+static cudaError_t launch(const Geo& geo, int grid, cudaStream_t st, const uint8_t* w, int N, int K, const void* x, int64_t ldx, int M,
+                          void* y, int y_dtype, uint8_t* ws, const WsLayout& l, const PeerPublish& pp, int* status) {
   static std::atomic<bool> attr_done[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -653,22 +665,23 @@ static cudaError_t launch(const Geo& geo, int grid, cudaStream_t st, const uint8
     attr_done[dev].store(true, std::memory_order_release);
   }
   constexpr int XR = 8 * NT;
-  cudaError_t err = launch_pdl(prepare_kernel<F, XR>, XR, 256, 0, st, (const __nv_bfloat16*)x, K, M, ws + l.xp, ws + l.xo,
-                               reinterpret_cast<int*>(ws + l.scol));
+  cudaError_t err = launch_pdl(prepare_kernel<F, XR>, XR, 256, 0, st, (const __nv_bfloat16*)x, ldx, K, M, ws + l.xp, ws + l.xo,
+                               reinterpret_cast<int*>(ws + l.scol), pp, status);
   if (err != cudaSuccess) return err;
   err = launch_pdl(gemv_wide_kernel<F, NT>, grid, kThreads, (size_t)geo.total, st, w, N, K, (const uint8_t*)(ws + l.xp),
                    (const uint8_t*)(ws + l.xo), reinterpret_cast<const int*>(ws + l.scol), M, y, y_dtype,
-                   reinterpret_cast<int*>(ws + kWsCounterOffset), reinterpret_cast<float*>(ws + l.slots), geo);
+                   reinterpret_cast<int*>(ws + kWsCounterOffset), reinterpret_cast<float*>(ws + l.slots), geo, pp);
   return err != cudaSuccess ? err : cudaPeekAtLastError();
 }
 
 template <class F>
 static cudaError_t launch_tiles(int NT, const Geo& geo, int grid, cudaStream_t st, const uint8_t* w, int N, int K, const void* x,
-                                int M, void* y, int y_dtype, uint8_t* ws, const WsLayout& l) {
+                                int64_t ldx, int M, void* y, int y_dtype, uint8_t* ws, const WsLayout& l, const PeerPublish& pp,
+                                int* status) {
   switch (NT) {
-    case 1: return launch<F, 1>(geo, grid, st, w, N, K, x, M, y, y_dtype, ws, l);
-    case 2: return launch<F, 2>(geo, grid, st, w, N, K, x, M, y, y_dtype, ws, l);
-    default: return launch<F, 4>(geo, grid, st, w, N, K, x, M, y, y_dtype, ws, l);
+    case 1: return launch<F, 1>(geo, grid, st, w, N, K, x, ldx, M, y, y_dtype, ws, l, pp, status);
+    case 2: return launch<F, 2>(geo, grid, st, w, N, K, x, ldx, M, y, y_dtype, ws, l, pp, status);
+    default: return launch<F, 4>(geo, grid, st, w, N, K, x, ldx, M, y, y_dtype, ws, l, pp, status);
   }
 }
 
@@ -696,7 +709,7 @@ size_t gemv_wide_workspace_bytes(int qtype, int64_t N, int64_t K, int M, int sm_
 }
 
 cudaError_t gemv_wide(int qtype, const uint8_t* w, int64_t N, int64_t K, const void* x, int M, void* y, int y_dtype,
-                      void* ws, size_t ws_bytes, int sm_count, cudaStream_t st) {
+                      void* ws, size_t ws_bytes, int sm_count, cudaStream_t st, int64_t ldx, const PeerPublish* peers, int* status) {
   using namespace wide;
   FormatInfo fi;
   if (!format_of(qtype, &fi)) return cudaErrorInvalidValue;
@@ -709,10 +722,14 @@ cudaError_t gemv_wide(int qtype, const uint8_t* w, int64_t N, int64_t K, const v
   const int grid = (int)std::min<int64_t>((int64_t)sm_count * kCtasPerSm, geo.S);
   const int NT = tiles_of(M);
   uint8_t* base = reinterpret_cast<uint8_t*>(ws);
+  PeerPublish pp = {};
+  if (peers) pp = *peers;
+  if (ldx <= 0) ldx = K;
+  if (ldx < K || (ldx * 2) % 16) return cudaErrorInvalidValue;
   switch (qtype) {
-    case QT_Q4_K: return launch_tiles<FQ4K>(NT, geo, grid, st, w, (int)N, (int)K, x, M, y, y_dtype, base, l);
-    case QT_Q5_K: return launch_tiles<FQ5K>(NT, geo, grid, st, w, (int)N, (int)K, x, M, y, y_dtype, base, l);
-    case QT_Q6_K: return launch_tiles<FQ6K>(NT, geo, grid, st, w, (int)N, (int)K, x, M, y, y_dtype, base, l);
+    case QT_Q4_K: return launch_tiles<FQ4K>(NT, geo, grid, st, w, (int)N, (int)K, x, ldx, M, y, y_dtype, base, l, pp, status);
+    case QT_Q5_K: return launch_tiles<FQ5K>(NT, geo, grid, st, w, (int)N, (int)K, x, ldx, M, y, y_dtype, base, l, pp, status);
+    case QT_Q6_K: return launch_tiles<FQ6K>(NT, geo, grid, st, w, (int)N, (int)K, x, ldx, M, y, y_dtype, base, l, pp, status);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -121,7 +121,14 @@ class PeerOutput:
         if n_out > self.n_total:
             raise ValueError(f"{self.world} shards of {w_shard.shape[0]} rows exceed the buffers' {self.n_total} columns")
         k = w_shard.shape[1]
-        xm = x.reshape(-1, k).contiguous()
+        # a 2-D view with unit inner stride is passed as it is (row stride = ldx): slicing the leading columns of an
+        # earlier exchange's buffer must not launch a copy, which would read the buffer before the peers' stores have landed
+        if x.dim() == 2 and x.stride(1) == 1 and x.shape[0] > 1 and x.stride(0) >= k and (x.stride(0) * 2) % 16 == 0 \
+                and x.data_ptr() % 16 == 0:
+            xm, ldx = x, x.stride(0)
+        else:
+            xm = x.reshape(-1, k).contiguous()
+            ldx = k
         m = xm.shape[0]
         if m > self.max_batch:
             raise ValueError(f"batch {m} exceeds the buffers' {self.max_batch}")
@@ -132,8 +139,8 @@ class PeerOutput:
         self._turn = (turn + 1) % len(self._bufs)
         with torch.cuda.device(dev):
             ws = _backend.workspace(dev, L.ggq_workspace_bytes(int(w_shard.qtype), w_shard.shape[0], k, m))
-            _lib.check(L.ggq_gemv_sharded(
-                int(w_shard.qtype), w_shard.data.data_ptr(), w_shard.shape[0], k, xm.data_ptr(), m,
+            _lib.check(L.ggq_gemm_sharded(
+                int(w_shard.qtype), w_shard.data.data_ptr(), w_shard.shape[0], k, xm.data_ptr(), ldx, m,
                 self._buf_ptrs[turn], self._flag_ptrs, self.world, self.rank, n_out,
                 _backend.dtype_code(self.dtype), 1 if wait_previous else 0,
                 ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,

@@ -180,6 +180,17 @@ int32_t ggq_gemv_sharded_tagged(int32_t qtype, const void* w, int64_t N_local, i
                                 int32_t rank, int64_t n_total, void* workspace,
                                 size_t workspace_bytes, void* stream);
 
+/* ggq_gemv_sharded for batches: M >= 1 rows of x, `ldx` elements apart (ldx >= K: x may be the leading K columns of a
+ * wider buffer, e.g. of an earlier exchange's output), Q4_K / Q5_K / Q6_K shards with K % 256 == 0 and 16-byte aligned
+ * rows.  y_peers[p] is rank p's (M, n_total) output; this rank's kernel stores its N_local columns of every batch row
+ * into all of them and raises its flag once per launch.  Batches above 32 rows run as slices of 32, one exchange each;
+ * a consumer that waits for the previous exchange (wait_previous of the next call) has all slices.  M == 1 is
+ * ggq_gemv_sharded.  Needs ggq_workspace_bytes(qtype, N_local, K, M).  No reference counterpart. */
+int32_t ggq_gemm_sharded(int32_t qtype, const void* w, int64_t N_local, int64_t K, const void* x_bf16, int64_t ldx,
+                         int32_t M, void* const* y_peers, uint32_t* const* flag_peers, int32_t world, int32_t rank,
+                         int64_t n_total, int32_t y_dtype, int32_t wait_previous, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
 /* Batch-1 Q4_K multiply that needs no scratch from the caller and allocates nothing.
  * No counterpart in the reference.  It exists for hosts that cannot allocate device memory
  * around a call: a custom-call handler whose framework owns every buffer, a serving loop

@@ -102,6 +102,50 @@ def main():
         fst.synchronize()
         check_flag_chain(f_outs, f"graph replay {rep}")
 
+    # flag exchange with a batch (ggq_gemm_sharded, batch-major kernel): a chain of products of 12 and of 40 rows (two slices),
+    # one of which reads only the leading columns of its predecessor's buffer (row stride larger than K, no copy)
+    os.environ["GGQ_GEMM_KERNEL"] = "wide"       # the one-GPU reference above 32 rows: the same exact kernel, not the bf16-weight GEMM
+    bk = 2048
+    bshapes = [(QT.Q4_K, 4096, bk), (QT.Q6_K, 2048, 2048), (QT.Q5_K, 2048, 2048), (QT.Q6_K, 2048, 2048)]   # (qtype, rows, K)
+    b_full = [gj.QuantizedArray.from_bytes(synth.make_weight_bytes(nn, kk, qt, seed=80 + i), qt, shape=(nn, kk), device=dev)
+              for i, (qt, nn, kk) in enumerate(bshapes)]
+    b_shards = [sharded.shard_rows(w, rank, world) for w in b_full]
+    keep = []            # nothing symmetric is freed while a later iteration captures a graph
+    for mb in (12, 40):
+        bout = sharded.PeerOutput(None, max_batch=mb, n_total=4096, device=dev, n_buffers=len(bshapes))
+        bx0 = torch.from_numpy(synth.make_x(mb, bk, seed=81)).to(dev).to(torch.bfloat16)
+
+        def run_batch_chain():
+            ys, cur = [], bx0
+            for i, sh in enumerate(b_shards):
+                cur = bout.matmul(cur[:, :sh.shape[1]], sh, wait_previous=i > 0)      # launch 1 reads 2048 of 4096 columns
+                ys.append(cur)
+            return ys
+
+        def check_batch_chain(ys, what):
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            vals = [y.clone() for y in ys]
+            for i, w in enumerate(b_full):
+                xin = bx0 if i == 0 else vals[i - 1][:, :w.shape[1]].contiguous()
+                same(vals[i], kernels.fused_matmul(xin, w), f"rank {rank}: batch {mb} flag chain {what}, launch {i}")
+            dist.barrier()
+
+        check_batch_chain(run_batch_chain(), "eager")
+        bst = torch.cuda.Stream(dev)
+        with torch.cuda.stream(bst):
+            bg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(bg, stream=bst):
+                b_outs = run_batch_chain()
+        for rep in range(2):
+            with torch.cuda.stream(bst):
+                bg.replay()
+            bst.synchronize()
+            check_batch_chain(b_outs, f"graph replay {rep}")
+        keep.append((bout, bg, b_outs, run_batch_chain, check_batch_chain))
+    del os.environ["GGQ_GEMM_KERNEL"]
+
     # tagged exchange: a chain whose products feed each other (n = k), including a result consumed
     # two launches later, then the same chain captured in a CUDA graph and replayed
     chain = [QT.Q4_K, QT.Q6_K, QT.Q5_K, QT.Q6_K, QT.Q4_K]
