@@ -3,6 +3,10 @@
 
 #include "ggq_common.cuh"
 
+#include <cuda.h>
+
+#include <atomic>
+
 namespace ggq {
 
 // Single rounding of a float32 result to the caller's output dtype.
@@ -11,6 +15,64 @@ __device__ __forceinline__ void store_out(void* y, int y_dtype, int64_t idx, flo
   else if (y_dtype == GGQ_BF16) reinterpret_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
   else reinterpret_cast<__half*>(y)[idx] = __float2half_rn(v);
 }
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against the driver library); null if the
+// driver does not offer it.  Used for the TMA copy paths; every user keeps a cp.async path for that case.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn tensor_map_encoder() {
+  static std::atomic<void*> cached{nullptr};
+  static std::atomic<bool> tried{false};
+  if (!tried.load(std::memory_order_acquire)) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    (void)cudaGetLastError();
+    cached.store(fn, std::memory_order_release);
+    tried.store(true, std::memory_order_release);
+  }
+  return reinterpret_cast<EncodeTiledFn>(cached.load(std::memory_order_acquire));
+}
+// A weight of `row_bytes` bytes per row (a multiple of 16) as a tensor map of 32-bit words [N rows, row_bytes / 4], box
+// = box_words x 16 rows, no swizzle, zeros outside the tensor.  False if there is no encoder or it refuses.
+inline bool make_weight_map(CUtensorMap* map, const uint8_t* w, int64_t N, int64_t row_bytes, int box_words) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (!fn || row_bytes % 16 || (uintptr_t)w % 16) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 4), (cuuint64_t)N};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)box_words, 16};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(w), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+#ifdef __CUDACC__
+// One lane: expect `bytes` on the mbarrier at shared address `bar`, then copy the box at word column x, row y of `map`
+// to shared address `dst` (128-byte aligned).  x * 4 must be a multiple of 16.
+__device__ __forceinline__ void tma_box_load(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar, uint32_t bytes) {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the slot's last reads precede the copy
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// All lanes: bounded wait for the phase `parity` of the mbarrier at `bar`; raises the status word when it runs out.
+__device__ __forceinline__ void tma_box_wait(uint32_t bar, uint32_t parity, int* status, int lane) {
+  uint32_t ok = 0;
+  for (uint32_t spin = 0; spin < (1u << 20) && !ok; spin++)
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  if (!ok && status && lane == 0) atomicOr(status, STATUS_WAIT_EXPIRED);
+}
+__device__ __forceinline__ void tma_bars_init(uint32_t bars, int n, int lane) {
+  if (lane == 0) {
+    for (int d = 0; d < n; d++) asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bars + 8 * d), "r"(1u) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+}
+#endif
 
 // Coverage kernel: any block qtype, any M <= 16 (gemv_generic.cu).
 cudaError_t gemv_generic(const TypeInfo* ti, const uint8_t* w, int64_t N, int64_t K, const void* x, int M,

@@ -523,26 +523,6 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
 
 }  // namespace q4k
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against the driver library); null if absent.
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn tensor_map_encoder() {
-  static std::atomic<void*> cached{nullptr};
-  static std::atomic<bool> tried{false};
-  if (!tried.load(std::memory_order_acquire)) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
-      fn = nullptr;
-    (void)cudaGetLastError();
-    cached.store(fn, std::memory_order_release);
-    tried.store(true, std::memory_order_release);
-  }
-  return reinterpret_cast<EncodeTiledFn>(cached.load(std::memory_order_acquire));
-}
-
 bool gemv_q4k_applicable(int64_t N, int64_t K, int M, const void* w, const void* x) {
   return M == 1 && K % 256 == 0 && q4k::Smem(2).total((int)K) <= q4k::kSmemLimit && N >= 1 &&
          N <= (1ll << 24) && N * (K / 256 * 144) < (1ll << 40) && (uintptr_t)w % 16 == 0 && (uintptr_t)x % 16 == 0;
@@ -599,16 +579,7 @@ cudaError_t gemv_q4k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
   memset(&w_map, 0, sizeof(w_map));
   static const bool want_tma = [] { const char* e = getenv("GGQ_Q4K_TMA"); return !(e && e[0] == '0'); }();
   bool tma = false;
-  if (want_tma && kSbPerWarp == 2) {
-    if (auto fn = tensor_map_encoder()) {
-      const cuuint64_t dims[2] = {(cuuint64_t)SB * (kBlockBytes / 4), (cuuint64_t)N};
-      const cuuint64_t strides[1] = {(cuuint64_t)SB * kBlockBytes};
-      const cuuint32_t box[2] = {(cuuint32_t)(kSlotPitch / 4), 16};
-      const cuuint32_t elem[2] = {1, 1};
-      tma = fn(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(w), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-    }
-  }
+  if (want_tma && kSbPerWarp == 2) tma = make_weight_map(&w_map, w, N, (int64_t)SB * kBlockBytes, kSlotPitch / 4);
   cudaError_t err;
 #define GGQ_Q4K_LAUNCH(D, T) launch_pdl(gemv_q4k_m1_kernel<D, T>, grid, kThreads, smem, st, w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status, w_map)
   if (tma) err = depth == 4 ? GGQ_Q4K_LAUNCH(4, true) : depth == 3 ? GGQ_Q4K_LAUNCH(3, true) : GGQ_Q4K_LAUNCH(2, true);

@@ -17,6 +17,9 @@
 // row, pitch 208 = 80 mod 128 so the 128-bit reads of a quarter-warp hit distinct banks).
 #include "gemv.cuh"
 
+#include <cstdlib>
+#include <cstring>
+
 namespace ggq {
 namespace q5k {
 
@@ -39,7 +42,8 @@ struct Smem {
   __host__ __device__ int zero(int K) const { return xs(K) + (K / 32) * 4; }     // 64 zero bytes
   __host__ __device__ int red(int K) const { return zero(K) + 64; }              // float[2][kWarps][16]
   __host__ __device__ int misc(int K) const { return red(K) + 2 * kWarps * 16 * 4; }
-  __host__ __device__ int total(int K) const { return misc(K) + 16; }
+  __host__ __device__ int bars(int K) const { return misc(K) + 16; }   // uint64[kWarps][4]: per-warp slot barriers (tensor-map copies)
+  __host__ __device__ int total(int K) const { return bars(K) + kWarps * 4 * 8; }
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -146,11 +150,13 @@ __device__ __forceinline__ void compute_tile(uint32_t tile, int g, int t, const 
   out1 = fmaf(dlb, fmaf(f_hi, hib[3], hi[3]), out1); out1 = fmaf(dmb, sx.y, out1);
 }
 
-template <int DEPTH>
+// TMA: a step's 16 rows x 208 bytes (the block and the 32 bytes behind it, which keep the slot's row pitch) arrive as one
+// two-dimensional tensor-map box issued by one lane, as in gemv_q4k.cu.
+template <int DEPTH, bool TMA>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloat16* __restrict__ x,
                    void* __restrict__ y, int y_dtype, int* __restrict__ counters, float* __restrict__ partials,
-                   const PeerPublish pp, int* __restrict__ status) {
+                   const PeerPublish pp, int* __restrict__ status, const __grid_constant__ CUtensorMap w_map) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -169,6 +175,8 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
 
   const Smem L(DEPTH);
   const uint32_t my_ring = smem_u32(smem) + warp * (DEPTH * kSlotBytes);
+  const uint32_t my_bars = smem_u32(smem) + L.bars(K) + warp * 32;        // DEPTH (<= 4) barriers of 8 bytes
+  if (TMA && warp < kWarps) tma_bars_init(my_bars, DEPTH, lane);
 
   // ---- copy side: 8 instructions per step, each copying the 11 pieces of two rows ----
   const int hl = lane >> 4, kl = lane & 15;
@@ -182,6 +190,18 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
   };
   seek_row_group();
   auto issue_next = [&]() {
+    if (TMA) {
+      if (issued < n_units) {
+        // words and rows outside the tensor (a chunk past the end of a ragged row, rows past N) arrive as zeros
+        if (lane == 0)
+          tma_box_load(my_ring + slot_i * kSlotBytes, &w_map, (c_i * kSbPerUnit + j) * (kBlockBytes / 4),
+                       rg_i * kRowsPerUnit + 16 * rt, my_bars + 8 * slot_i, (uint32_t)kSlotBytes);
+        ++issued;
+        if (++slot_i == DEPTH) slot_i = 0;
+        if (++c_i == C) { c_i = 0; ++rg_i; }
+      }
+      return;
+    }
     if (issued < n_units) {
       const uint32_t dst = my_ring + slot_i * kSlotBytes;
       const int row0 = rg_i * kRowsPerUnit + 16 * rt;
@@ -310,6 +330,7 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
   // (hand-off through two pairs of named barriers, as in gemv_q4k.cu).
   if (tile_warp) {
     int rg = rg_begin, c = c_begin, done = 0, slot = 0, flush_i = 0;
+    uint32_t ring_round = 0;                               // how often the ring has wrapped: the parity the slot's barrier shows
     while (done < n_units) {
       const int c_first = c;
       const int c_stop = min(C, c + (n_units - done));
@@ -319,11 +340,12 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
       uint32_t xsa = xs_lane_base + (uint32_t)sbg * 32u;
       for (; c < c_stop; ++c) {
         issue_next();
-        cp_async_wait<DEPTH - 1>();
+        if (TMA) tma_box_wait(my_bars + 8 * slot, ring_round & 1, status, lane);
+        else cp_async_wait<DEPTH - 1>();
         __syncwarp();
         if (sbg < SB) compute_tile(my_ring + slot * kSlotBytes, g, t, lc, m1, f_lo, f_hi, xa, x_step, xsa, out0, out1);
         __syncwarp();
-        if (++slot == DEPTH) slot = 0;
+        if (++slot == DEPTH) { slot = 0; ++ring_round; }
         sbg += kSbPerUnit;
         xa += kSbPerUnit * x_sb_stride;
         xsa += kSbPerUnit * 32u;
@@ -391,7 +413,7 @@ gemv_q5k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
       if (c == C) { c = 0; ++rg; }
     }
   }
-  cp_async_wait<0>();
+  if (!TMA) cp_async_wait<0>();
   peer_publish(pp, tid, G);
 }
 
@@ -419,19 +441,28 @@ cudaError_t gemv_q5k(const uint8_t* w, int64_t N, int64_t K, const void* x, void
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    cudaError_t e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_q5k_m1_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return e;
     attr_done[dev].store(true, std::memory_order_release);
   }
   float* partials = reinterpret_cast<float*>(ws);
   int* counters = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ws) + kWsCounterOffset);
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+  // copy path: tensor-map boxes where the driver offers the encoder (GGQ_Q5K_TMA=0 keeps cp.async, also the fallback)
+  alignas(64) CUtensorMap w_map;
+  memset(&w_map, 0, sizeof(w_map));
+  static const bool want_tma = [] { const char* e = getenv("GGQ_Q5K_TMA"); return !(e && e[0] == '0'); }();
+  const bool tma = want_tma && make_weight_map(&w_map, w, N, K / 256 * kBlockBytes, kSlotPitch / 4);
   cudaError_t err;
-  if (depth == 4) err = launch_pdl(gemv_q5k_m1_kernel<4>, grid, kThreads, smem, st, w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
-  else if (depth == 3) err = launch_pdl(gemv_q5k_m1_kernel<3>, grid, kThreads, smem, st, w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
-  else err = launch_pdl(gemv_q5k_m1_kernel<2>, grid, kThreads, smem, st, w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status);
+#define GGQ_Q5K_LAUNCH(D, T) launch_pdl(gemv_q5k_m1_kernel<D, T>, grid, kThreads, smem, st, w, (int)N, (int)K, xb, y, y_dtype, counters, partials, pp, status, w_map)
+  if (tma) err = depth == 4 ? GGQ_Q5K_LAUNCH(4, true) : depth == 3 ? GGQ_Q5K_LAUNCH(3, true) : GGQ_Q5K_LAUNCH(2, true);
+  else err = depth == 4 ? GGQ_Q5K_LAUNCH(4, false) : depth == 3 ? GGQ_Q5K_LAUNCH(3, false) : GGQ_Q5K_LAUNCH(2, false);
+#undef GGQ_Q5K_LAUNCH
   return err != cudaSuccess ? err : cudaPeekAtLastError();
 }
 
