@@ -3,7 +3,7 @@
 // Data movement.  A persistent CTA per SM with sixteen tile warps (and a seventeenth that only
 // reduces and publishes row sums, see the multiply side).  Every warp streams its own
 // steps (16 weight rows x two adjacent 144-byte superblocks, 4.6 KB) from HBM into a private
-// ring of shared-memory slots with 16-byte cp.async copies, one to three steps ahead of the
+// ring of shared-memory slots, one to three steps ahead of the
 // one it is multiplying (as many as shared memory allows next to the staged activations; no
 // registers are held by loads in flight); the warps of a CTA sit on adjacent superblocks of
 // the same 32 rows, so each row is read as a contiguous run.  A step arrives either as one

@@ -11,7 +11,8 @@
 // (qh & (0x00020002 << 2t)) -- single bits, so the masked word is a valid bf16 pair whatever the
 // bit position -- accumulated in tiles of their own and folded with a per-lane power of two:
 //     u = nib + f * bit,      y += (d * sc) * u - (dmin * mn) * sum(x).
-// Everything else (persistent CTA per SM, per-warp cp.async rings, activations staged once as
+// Everything else (persistent CTA per SM, per-warp rings filled by one TMA box per step -- 52 words x 16 rows --
+// or by cp.async where no tensor-map encoder is to be had, activations staged once as
 // scaled pair-permuted bf16, the eight B columns as eight sub-block channels, contiguous unit
 // ranges with a last-arriver reduction) is the Q4_K design; a step is one superblock (176 B per
 // row, pitch 208 = 80 mod 128 so the 128-bit reads of a quarter-warp hit distinct banks).

@@ -26,7 +26,9 @@
 //
 // Data movement.  Persistent CTA per SM, sixteen tile warps (plus a reducer warp, as in
 // gemv_q4k.cu), each streaming its own tiles (16 rows
-// x one superblock) into a private ring of shared-memory slots with 16-byte cp.async copies.
+// x one superblock) into a private ring of shared-memory slots: one two-dimensional TMA box per step (72 words x 16
+// rows of a tensor map over the weight, issued by one lane, counted on a per-warp mbarrier; 45.7 against 49.2 us on
+// 8192 x 28672), or 16-byte cp.async copies where the driver offers no tensor-map encoder.
 // A 210-byte block is only 2-byte aligned, so a step copies the 16-byte aligned window of 224
 // bytes that contains the block and the multiply reads its fields at the block's offset in that
 // window (skew); warp j always works on superblocks j, j+8, ... whose skew 2j mod 16 is constant.
