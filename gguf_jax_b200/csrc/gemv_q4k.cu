@@ -361,15 +361,22 @@ gemv_q4k_m1_kernel(const uint8_t* __restrict__ w, int N, int K, const __nv_bfloa
         amax = fmaxf(amax, asum);
       
       };
-      auto rotated = [&](int i) { int sblk = i + rot; return sblk >= n_sub ? sblk - n_sub : sblk; };
-      for (int i = tid; i < n_sub; i += 2 * kThreads) {
+      // A CTA whose units cover fewer chunks than a row has (small shards, small weights) stages only those chunks:
+      // `count` sub-blocks from the first chunk on, wrapping at the end of the padded row (C whole chunks); places
+      // past the real end of a row are skipped.  Otherwise all of x, from the rotated start.
+      const bool part = n_units < C;
+      const int wrap = part ? C * (kSbPerUnit * 8) : n_sub;
+      const int first = part ? c_begin * (kSbPerUnit * 8) : rot;
+      const int count = part ? n_units * (kSbPerUnit * 8) : n_sub;
+      auto rotated = [&](int i) { int sblk = i + first; return sblk >= wrap ? sblk - wrap : sblk; };
+      for (int i = tid; i < count; i += 2 * kThreads) {
         const int s0 = rotated(i), i1 = i + kThreads;
-        const bool two = i1 < n_sub;
-        const int s1 = two ? rotated(i1) : s0;
+        const int s1 = i1 < count ? rotated(i1) : n_sub;
+        const bool one = s0 < n_sub, two = s1 < n_sub;
         uint4 v0[4], v1[4];
-        fetch(s0, v0);
+        if (one) fetch(s0, v0);
         if (two) fetch(s1, v1);
-        convert(s0, v0);
+        if (one) convert(s0, v0);
         if (two) convert(s1, v1);
       }
       return amax;
