@@ -21,10 +21,14 @@ pytestmark = pytest.mark.gpu
 WIDE = [QT.Q4_K, QT.Q5_K, QT.Q6_K]
 
 
-@pytest.fixture(autouse=True)
-def _batch_major_kernel_for_every_batch(monkeypatch):
-    # above 32 rows ggq_gemm would otherwise pick the bf16-weight tcgen05 kernel
+@pytest.fixture(autouse=True, params=["tma_boxes", "cp_async"])
+def _batch_major_kernel_for_every_batch(monkeypatch, request):
+    # above 32 rows ggq_gemm would otherwise pick the bf16-weight tcgen05 kernel; every test runs with the weight
+    # slots copied as TMA boxes and as per-lane cp.async (the library reads the switch on every call)
     monkeypatch.setenv("GGQ_GEMM_KERNEL", "wide")
+    monkeypatch.setenv("GGQ_WIDE_TMA", "1" if request.param == "tma_boxes" else "0")
+
+
 BIG = (6144, 6144)            # 21 to 31 MB in these formats: above the size from which ggq_gemv picks this kernel
 
 
