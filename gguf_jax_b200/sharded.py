@@ -172,24 +172,31 @@ class TaggedExchange:
     Each launch stores its rows into every rank's buffer as self-validating 32-bit words (bf16
     value + 16-bit tag of the exchange); a later launch that takes a :class:`TaggedVector` as its
     activation polls the words it needs until they carry the expected tag.  Buffers are used
-    round-robin: a result may be consumed by the next ``n_buffers - 2`` launches at most.  All
+    round-robin.  A CTA polls only the chunks of the activation vector that its share of the weight
+    touches, so it may store its outputs before another rank's part of that vector has landed; what
+    bounds how far one rank runs ahead of another is that a launch starts only after the previous
+    launch of its own rank has finished, i.e. has seen the whole of *its* activations.  With results
+    consumed at most ``max_back`` launches later, a rank storing exchange e can therefore meet a peer
+    still reading exchange ``e - 2 * max_back``: two uses of a buffer must lie at least
+    ``2 * max_back + 1`` launches apart (``n_buffers >= 2 * max_back + 1``).  All
     ranks must issue the same sequence of launches.  Tags are derived on the device from a
     per-rank launch counter, so a captured CUDA graph of a whole chain can be replayed.
     Supported: Q4_K, Q5_K and Q6_K weights at batch 1 (the tuned kernels' shapes).
 
     Replaying a captured chain of L launches repeats its buffer sequence, so the round-robin must
     stay intact across the seam: pick ``n_buffers`` with ``L % n_buffers == 0`` or
-    ``L % n_buffers >= 4`` (:meth:`buffers_for` does).
+    ``L % n_buffers >= 2 * max_back + 1`` (:meth:`buffers_for` does).
     """
 
     @staticmethod
     def buffers_for(chain_length: int, max_back: int = 2) -> int:
-        """Smallest buffer count that keeps every reuse ``max_back + 2`` launches apart when a
-        chain of ``chain_length`` launches is replayed back to back."""
-        for nb in range(max_back + 2, 17):
-            if chain_length % nb == 0 or chain_length % nb >= max_back + 2:
+        """Smallest buffer count (at least 3) that keeps every reuse ``2 * max_back + 1`` launches apart
+        when a chain of ``chain_length`` launches is replayed back to back."""
+        apart = max(3, 2 * max_back + 1)
+        for nb in range(apart, 33):
+            if chain_length % nb == 0 or chain_length % nb >= apart:
                 return nb
-        return max_back + 2
+        return apart
 
     def __init__(self, group, n_max: int, device=None, n_buffers: int = 4):
         import ctypes

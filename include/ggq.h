@@ -172,7 +172,10 @@ int32_t ggq_gemv_sharded(int32_t qtype, const void* w, int64_t N_local, int64_t 
  * after_words tagged words of the exchange after_back launches ago in this rank's own buffer:
  * the kernel does not read its activations before all of them have arrived, which orders it
  * after that exchange the way ggq_gemv_sharded's flags would.  All ranks must issue the same
- * sequence of calls; a buffer may be reused for a new exchange once x_back_max + 2 exchanges have passed. */
+ * sequence of calls.  A CTA polls only the part of the activations that its share of the weight touches, so
+ * a rank may store exchange e while a peer still reads exchange e - 2 * x_back_max: a buffer may be reused for a
+ * new exchange once 2 * x_back_max + 1 exchanges have passed (every call ordered with after_tagged behind the
+ * exchange before it: x_back_max + 2). */
 int32_t ggq_gemv_sharded_tagged(int32_t qtype, const void* w, int64_t N_local, int64_t K,
                                 const void* x_bf16, const uint32_t* x_tagged, int32_t x_back,
                                 const uint32_t* after_tagged, int64_t after_words,

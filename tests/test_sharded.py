@@ -70,15 +70,17 @@ def test_row_range_errors():
 
 
 def test_tagged_exchange_buffer_count_keeps_reuse_distance_across_replays():
-    """A replayed chain of L launches cycles through n buffers; launch j of the next replay must not
-    land on a buffer that one of the last max_back + 1 launches of the previous replay wrote."""
+    """A replayed chain of L launches cycles through n buffers; a launch must not land on a buffer that
+    one of the 2 * max_back launches before it wrote, across the seam of two replays as well (a rank may
+    store exchange e while a peer still reads exchange e - 2 * max_back)."""
     from gguf_jax_b200.sharded import TaggedExchange
     for length in [1, 2, 5, 6, 7, 12, 401, 402, 403, 404, 1000]:
         for max_back in (1, 2, 3):
             nb = TaggedExchange.buffers_for(length, max_back)
-            assert nb >= max_back + 2
+            apart = 2 * max_back + 1
+            assert nb >= apart
             seq = [(s % nb) for s in range(1, length + 1)] * 3      # three replays, host serials restart
             for i, b in enumerate(seq):
-                earlier = seq[max(0, i - (max_back + 1)):i]
-                if length > max_back + 1:
+                earlier = seq[max(0, i - (apart - 1)):i]
+                if length >= apart:
                     assert b not in earlier, (length, max_back, nb, i)
