@@ -911,7 +911,7 @@ def run_ours(args) -> None:
             line["legs"] = legs
         if cpu is not None:
             line["cpu_baseline"] = cpu
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)       # out of the process before any tear-down
     if world > 1:
         # Tear down without destroy_process_group(): with NCCL kernels captured in a CUDA graph it
         # has been seen to block at exit.  Everything is flushed and every rank has passed the
