@@ -818,16 +818,17 @@ def run_ours(args) -> None:
     e2e_steps = min(args.steps, 200)
 
     def e2e_step(i: int):
-        xd = xh.to(dev, non_blocking=True)
         if world > 1:
+            xd = xh.to(dev, non_blocking=True)
             # the public sharded call: local fused product, then the all-gather, all stream-ordered (the
             # in-kernel exchange orders launches against each other, not against a host read-back)
             y = gj.matmul(xd, weights[i % copies])
             dist.all_gather_into_tensor(y_full, y)
             yh.view(world, BATCH, rows_local).copy_(y_full, non_blocking=True)
         else:
-            y = gj.matmul(xd, weights[i % copies])
-            yh.copy_(y, non_blocking=True)
+            # one GPU: the public call takes the pinned host tensors themselves - the activations are fetched by a
+            # small kernel in front of the product (ggq_stage_host) and the product stores into the pinned result
+            gj.matmul(xh, weights[i % copies], out=yh)
         torch.cuda.current_stream().synchronize()
 
     for i in range(3):
@@ -845,6 +846,11 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     e2e_value = algorithmic_bytes(N_ROWS, K_DIM, BATCH) * e2e_steps / e2e_s / 1e9
+    if world == 1:
+        # what the last step left in the host buffer is the device-resident product, bit for bit
+        want = kernels.fused_matmul(x, weights[(e2e_steps - 1) % copies]).cpu()
+        if not torch.equal(yh, want):
+            raise RuntimeError("end-to-end leg: the host result differs from the device-resident product")
 
     decode = None
     if not args.no_decode:
@@ -904,7 +910,12 @@ def run_ours(args) -> None:
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * BATCH * K_DIM,
                     "d2h_bytes_per_step": 2 * BATCH * N_ROWS, "steps": e2e_steps,
                     "ms_per_step": e2e_s / e2e_steps * 1e3,
-                    "note": "weight resident on the device; activation H2D from pinned memory and result D2H every step"},
+                    "note": ("weight resident on the device; every step gguf_jax_b200.matmul(x_pinned, w, out=y_pinned): the activations "
+                             "are fetched from pinned host memory by a kernel in front of the product, the product stores its result "
+                             "into pinned host memory, then the stream is synchronised; the last result is checked against the "
+                             "device-resident product bit for bit") if world == 1 else
+                            "weight resident on the device; activation H2D from pinned memory, fused product on the shard, "
+                            "NCCL all-gather and result D2H every step, then the stream is synchronised"},
             "gpu_launches": args.steps * launches_per_step,
             "parity": parity,
         }

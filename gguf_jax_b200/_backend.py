@@ -12,6 +12,7 @@ from . import _lib
 
 _DTYPE_CODE = {torch.float32: _lib.GGQ_F32, torch.bfloat16: _lib.GGQ_BF16, torch.float16: _lib.GGQ_F16}
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_stagings: dict[tuple[int, int], torch.Tensor] = {}
 
 
 def canon_dtype(dtype) -> torch.dtype:
@@ -60,6 +61,16 @@ def require_cuda(t: torch.Tensor, what: str) -> int:
 
 def stream_ptr(device_index: int) -> int:
     return torch.cuda.current_stream(device_index).cuda_stream
+
+
+def staging(device_index: int, nbytes: int) -> torch.Tensor:
+    """Device buffer that receives host-resident activations, one per (device, stream), grown on demand.
+    Calls on one stream are ordered, so one buffer serves them all."""
+    key = (device_index, torch.cuda.current_stream(device_index).cuda_stream)
+    buf = _stagings.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = _stagings[key] = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=torch.device("cuda", device_index))
+    return buf
 
 
 def workspace(device_index: int, nbytes: int) -> torch.Tensor | None:

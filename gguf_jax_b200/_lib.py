@@ -61,6 +61,7 @@ SIGNATURES = {
     "ggq_gemv_q4k_static": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p,
                                              ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]),
     "ggq_read_status": (ctypes.c_int32, [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32)]),
+    "ggq_stage_host": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
 }
 
 

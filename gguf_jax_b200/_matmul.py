@@ -24,7 +24,7 @@ import torch
 from gguf.constants import GGML_QUANT_SIZES
 from gguf.constants import GGMLQuantizationType as QT
 
-from . import _lib, kernels
+from . import _backend, _lib, kernels
 from .array import QuantizedArray
 
 __all__ = ["dequant_matmul", "fused_batch_limit", "fused_types", "matmul"]
@@ -71,7 +71,7 @@ def _validate(x: torch.Tensor, w) -> None:
 
 
 def matmul(x: torch.Tensor, w: QuantizedArray, *, block_bytes: int | None = None,
-           force_fused: bool = False) -> torch.Tensor:
+           force_fused: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
     """``x (..., K) @ w(N, K).T -> (..., N)``.
 
     Fused when ``w.qtype`` has a kernel, ``x`` is bfloat16 and the flattened batch does not
@@ -80,6 +80,11 @@ def matmul(x: torch.Tensor, w: QuantizedArray, *, block_bytes: int | None = None
     else is materialized under the ``block_bytes`` budget (default
     :data:`DEQUANT_BLOCK_BYTES`).  ``TypeError`` for a weight that is not a
     :class:`QuantizedArray`, ``ValueError`` for a weight that is not 2-D or a contraction mismatch.
+
+    Host-resident operands (an extension; the reference's arrays are device arrays): ``x`` may be a
+    pinned CPU tensor and ``out`` a pinned CPU (or device) tensor of the result's shape.  They are
+    served by the fused route only (see :func:`gguf_jax_b200.kernels.fused_matmul`), without
+    gradients; anything the fused route does not take raises ``ValueError``.
     """
     _validate(x, w)
     route = None
@@ -88,6 +93,13 @@ def matmul(x: torch.Tensor, w: QuantizedArray, *, block_bytes: int | None = None
         batch = math.prod(x.shape[:-1])
         if force_fused or batch <= hit[1](w):
             route = hit[0]
+    if out is not None or not x.is_cuda:
+        _backend.require_cuda(w.data, "matmul")
+        if route is None:
+            raise ValueError("host-resident activations and caller-owned results are served by the fused kernels only "
+                             f"(bfloat16 x, a fused qtype, batch within fused_batch_limit); got {w.qtype.name}, {x.dtype}, "
+                             f"batch {math.prod(x.shape[:-1])}")
+        return route(x, w, out=out)
     return _apply(x, w, route, _slab_count(w, block_bytes))
 
 

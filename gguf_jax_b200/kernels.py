@@ -58,43 +58,74 @@ def _check(x: torch.Tensor, w: QuantizedArray, qtypes=None) -> tuple[int, int]:
     return n_rows, k_dim
 
 
-def fused_matmul(x: torch.Tensor, w: QuantizedArray, *, out_dtype=torch.bfloat16) -> torch.Tensor:
+def fused_matmul(x: torch.Tensor, w: QuantizedArray, *, out_dtype=torch.bfloat16, out: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ w.T`` through the fused kernels, whatever the batch: ``ggq_gemv`` up to
     ``gemv_max_batch()`` rows (tuned batch-1, tiled, batch-major or small-weight MMA kernel, chosen
     by the library per format, batch and weight size), ``ggq_gemm`` above it (Q4_K / Q5_K / Q6_K:
-    the batch-major kernel in slices of 32 rows up to 128 rows, then the integer-code tcgen05
-    kernel; other formats: the tf32 tcgen05 kernel)."""
+    the batch-major kernel up to 32 rows, then the bf16-weight tcgen05 kernel; other formats: the
+    tf32 tcgen05 kernel).
+
+    Host-resident operands: ``x`` may be a *pinned* CPU tensor (it is brought to the device by
+    ``ggq_stage_host``, a small kernel in front of the product, instead of a copy-engine transfer),
+    and ``out`` may be a pinned CPU tensor of the result's shape (up to ``gemv_max_batch()`` rows):
+    the kernel then stores the result straight into host memory, readable once the stream has been
+    synchronised.  Pageable host memory is refused; there is no CPU computation."""
     n_rows, k_dim = _check(x, w)
     dev = _backend.require_cuda(w.data, f"fused matmul ({w.qtype.name})")
-    if x.device != w.data.device:
+    host_x = not x.is_cuda
+    if host_x:
+        if not x.is_pinned():
+            raise RuntimeError("fused matmul: x lives in pageable host memory; pin it (x.pin_memory()) or move it to "
+                               "the device - the library computes on the GPU only")
+    elif x.device != w.data.device:
         raise ValueError(f"x is on {x.device}, w on {w.data.device}")
     _lib.ensure_tables(dev)
     L = _lib.lib()
-    out_dtype = _backend.canon_dtype(out_dtype)
     xm = x.reshape(-1, k_dim).contiguous()
     m = xm.shape[0]
-    data = w.data.contiguous()
-    y = torch.empty((m, n_rows), dtype=out_dtype, device=x.device)
-    if m == 0:
-        return y.reshape(*x.shape[:-1], n_rows)
-    fn = L.ggq_gemv if m <= _gemv_cap(L) else L.ggq_gemm
     # the common case (the tensors live on the current device) skips the device switch, which
     # costs more host time than the rest of this function
-    switch = torch.cuda.current_device() != dev
-    if switch:
-        prev = torch.cuda.current_device()
+    prev = torch.cuda.current_device()
+    if prev != dev:
         torch.cuda.set_device(dev)
     try:
+        stream = _backend.stream_ptr(dev)
+        x_ptr = xm.data_ptr()
+        if host_x and m > 0:
+            # first thing, so that the fetch runs on the GPU while the host prepares the product's launch
+            nbytes = m * k_dim * 2
+            xd = _backend.staging(dev, nbytes)
+            _lib.check(L.ggq_stage_host(x_ptr, xd.data_ptr(), nbytes, stream))
+            x_ptr = xd.data_ptr()
+        data = w.data.contiguous()
+        if out is not None:
+            if tuple(out.shape) != (*x.shape[:-1], n_rows) or not out.is_contiguous():
+                raise ValueError(f"out must be contiguous with shape {(*x.shape[:-1], n_rows)}, got {tuple(out.shape)}")
+            if out.is_cuda:
+                if out.device != w.data.device:
+                    raise ValueError(f"out is on {out.device}, w on {w.data.device}")
+            elif not out.is_pinned():
+                raise RuntimeError("fused matmul: out lives in pageable host memory; pin it or use a device tensor")
+            elif m > _gemv_cap(L):
+                raise ValueError(f"a host result buffer is served up to {_gemv_cap(L)} batch rows, got {m}")
+            out_dtype = out.dtype
+            y = out.view(m, n_rows)
+        else:
+            out_dtype = _backend.canon_dtype(out_dtype)
+            y = torch.empty((m, n_rows), dtype=out_dtype, device=w.data.device)
+        if m == 0:
+            return y.reshape(*x.shape[:-1], n_rows)
+        fn = L.ggq_gemv if m <= _gemv_cap(L) else L.ggq_gemm
         key = (int(w.qtype), n_rows, k_dim, m)
         need = _ws_need.get(key)
         if need is None:
             need = _ws_need[key] = L.ggq_workspace_bytes(*key)
         ws = _backend.workspace(dev, need)
-        _lib.check(fn(key[0], data.data_ptr(), n_rows, k_dim, xm.data_ptr(), m, y.data_ptr(),
+        _lib.check(fn(key[0], data.data_ptr(), n_rows, k_dim, x_ptr, m, y.data_ptr(),
                       _backend.dtype_code(out_dtype), ws.data_ptr() if ws is not None else None,
-                      ws.numel() if ws is not None else 0, _backend.stream_ptr(dev)))
+                      ws.numel() if ws is not None else 0, stream))
     finally:
-        if switch:
+        if prev != dev:
             torch.cuda.set_device(prev)
     return y.reshape(*x.shape[:-1], n_rows)
 

@@ -158,6 +158,18 @@ int32_t ggq_gemv_sharded(int32_t qtype, const void* w, int64_t N_local, int64_t 
                          int32_t rank, int64_t n_total, int32_t y_dtype, int32_t wait_previous,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* Activations and results in page-locked host memory (no counterpart in the reference, whose arrays are
+ * device-resident; what jax.device_put / device_get do around its calls).  In front of a 30 us product a
+ * copy-engine transfer costs about 12 us of latency each way; these two uses avoid it:
+ *  - ggq_stage_host copies `bytes` (a multiple of 16, both addresses 16-byte aligned, at most 64 MB) from a
+ *    page-locked, device-visible host buffer (cudaHostAlloc / cudaHostRegister under unified addressing) to device
+ *    memory with a small kernel that reads the host buffer over the bus; the product enqueued behind it is its
+ *    programmatic dependent and prefetches weight tiles meanwhile.  The host buffer must stay unchanged until the
+ *    stream has passed the call.
+ *  - `y` of ggq_gemv may itself be such a host buffer: the kernels only ever store to y, the stores are
+ *    visible to the host once the stream has been synchronised. */
+int32_t ggq_stage_host(const void* host_src, void* device_dst, size_t bytes, void* stream);
+
 /* Row-sharded batch-1 multiply with a tagged exchange: no flags and no fences.  No counterpart in
  * the reference.  Every output element is stored into every rank's buffer as one 32-bit word
  * (bf16 value in the low half, a 16-bit tag of the exchange in the high half), so each word
