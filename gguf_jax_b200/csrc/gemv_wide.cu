@@ -134,6 +134,7 @@ struct Geo {
   int xstage_bytes;           // XR * (512 + kOffBytes)
   int off_x, total;
   int tma;                    // weight slots arrive as TMA boxes (one per warp and step) instead of cp.async copies
+  int vec_store;              // 2-byte outputs whose 8-row runs are 16-byte aligned: stored as 16-byte vectors
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -542,6 +543,47 @@ gemv_wide_kernel(const uint8_t* __restrict__ w, int N, int K, const uint8_t* __r
     unscale[nt][1] = pow2f(133 - S_col[nt * 8 + 2 * t + 1]);
   }
   auto store_rows = [&](int rb, const float (&v)[NT][4]) {
+    const int row_base = rb * kBlockRows + warp * 16;
+    if (geo.vec_store && row_base + 16 <= N) {
+      // Turn the fragment layout (a lane holds 2 rows x 2 columns per column tile) into runs of 8 rows of one column
+      // with shuffles, so that every store is 16 bytes: a quarter of the store instructions and, row-sharded, NVLink
+      // packets of 16 and 32 bytes instead of 2-byte ones (the store phase is what grows with the ranks).
+      // Lanes 0..15 end up with (column c = lane / 2, row half h = lane & 1) of the column tile.
+      const int c = (lane >> 1) & 7, h = lane & 1;
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) {
+        const float a0 = v[nt][0] * unscale[nt][0], a1 = v[nt][1] * unscale[nt][1];
+        const float a2 = v[nt][2] * unscale[nt][0], a3 = v[nt][3] * unscale[nt][1];
+        uint32_t p0, p1;       // (column 2t, column 2t + 1) of row g and of row g + 8
+        if (y_dtype == GGQ_BF16) {
+          const __nv_bfloat162 q0 = __floats2bfloat162_rn(a0, a1), q1 = __floats2bfloat162_rn(a2, a3);
+          p0 = *reinterpret_cast<const uint32_t*>(&q0); p1 = *reinterpret_cast<const uint32_t*>(&q1);
+        } else {
+          const __half2 q0 = __floats2half2_rn(a0, a1), q1 = __floats2half2_rn(a2, a3);
+          p0 = *reinterpret_cast<const uint32_t*>(&q0); p1 = *reinterpret_cast<const uint32_t*>(&q1);
+        }
+        uint32_t e[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const int src = j * 4 + (c >> 1);            // the lane with g = j, t = c / 2
+          const uint32_t u0 = __shfl_sync(0xFFFFFFFFu, p0, src), u1 = __shfl_sync(0xFFFFFFFFu, p1, src);
+          const uint32_t u = h ? u1 : u0;
+          e[j] = (c & 1) ? (u >> 16) : (u & 0xFFFFu);
+        }
+        const uint4 run = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+        const int col = nt * 8 + c;
+        if (lane < 16 && col < M) {
+          if (pp.world == 0) {
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(y) + (int64_t)col * N + row_base + 8 * h) = run;
+          } else {
+#pragma unroll 1
+            for (int p = 0; p < pp.world; p++)
+              *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(pp.y[p]) + (int64_t)col * pp.n_total + pp.row_offset + row_base + 8 * h) = run;
+          }
+        }
+      }
+      return;
+    }
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
 #pragma unroll
@@ -751,6 +793,16 @@ cudaError_t gemv_wide(int qtype, const uint8_t* w, int64_t N, int64_t K, const v
   CUtensorMap w_map;
   memset(&w_map, 0, sizeof(w_map));
   geo.tma = want_tma && make_weight_map(&w_map, w, N, K / 256 * fi.ts, fi.pitch / 4) ? 1 : 0;
+  // 16-byte output stores: 2-byte outputs, and every run of 8 rows of a column starts on a 16-byte boundary
+  bool vec = y_dtype == GGQ_BF16 || y_dtype == GGQ_F16;
+  if (pp.world == 0) {
+    vec = vec && N % 8 == 0 && (uintptr_t)y % 16 == 0;
+  } else {
+    vec = vec && pp.n_total % 8 == 0 && pp.row_offset % 8 == 0;
+    for (int p = 0; p < pp.world; p++) vec = vec && (uintptr_t)pp.y[p] % 16 == 0;
+  }
+  const char* vec_env = getenv("GGQ_WIDE_VEC_STORE");       // "0": element-wise stores (read per call; the tests take both)
+  geo.vec_store = vec && !(vec_env && vec_env[0] == '0') ? 1 : 0;
   switch (qtype) {
     case QT_Q4_K: return launch_tiles<FQ4K>(NT, geo, grid, st, w, (int)N, (int)K, x, ldx, M, y, y_dtype, base, l, pp, status, w_map);
     case QT_Q5_K: return launch_tiles<FQ5K>(NT, geo, grid, st, w, (int)N, (int)K, x, ldx, M, y, y_dtype, base, l, pp, status, w_map);

@@ -27,6 +27,8 @@ def _batch_major_kernel_for_every_batch(monkeypatch, request):
     # slots copied as TMA boxes and as per-lane cp.async (the library reads the switch on every call)
     monkeypatch.setenv("GGQ_GEMM_KERNEL", "wide")
     monkeypatch.setenv("GGQ_WIDE_TMA", "1" if request.param == "tma_boxes" else "0")
+    # likewise the output stores: 16-byte runs (default) with the boxes, element-wise with cp.async
+    monkeypatch.setenv("GGQ_WIDE_VEC_STORE", "1" if request.param == "tma_boxes" else "0")
 
 
 BIG = (6144, 6144)            # 21 to 31 MB in these formats: above the size from which ggq_gemv picks this kernel
