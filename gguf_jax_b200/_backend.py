@@ -63,22 +63,24 @@ def stream_ptr(device_index: int) -> int:
     return torch.cuda.current_stream(device_index).cuda_stream
 
 
-def staging(device_index: int, nbytes: int) -> torch.Tensor:
+def staging(device_index: int, nbytes: int, stream: int | None = None) -> torch.Tensor:
     """Device buffer that receives host-resident activations, one per (device, stream), grown on demand.
-    Calls on one stream are ordered, so one buffer serves them all."""
-    key = (device_index, torch.cuda.current_stream(device_index).cuda_stream)
+    Calls on one stream are ordered, so one buffer serves them all.  ``stream``: the current stream's handle if
+    the caller already has it."""
+    key = (device_index, stream_ptr(device_index) if stream is None else stream)
     buf = _stagings.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = _stagings[key] = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=torch.device("cuda", device_index))
     return buf
 
 
-def workspace(device_index: int, nbytes: int) -> torch.Tensor | None:
+def workspace(device_index: int, nbytes: int, stream: int | None = None) -> torch.Tensor | None:
     """Zero-filled scratch for the fused kernels, one per (device, stream), grown on demand.
-    The kernels leave it zeroed, so it is cleared only when (re)allocated."""
+    The kernels leave it zeroed, so it is cleared only when (re)allocated.  ``stream``: the current stream's
+    handle if the caller already has it."""
     if nbytes == 0:
         return None
-    key = (device_index, stream_ptr(device_index))
+    key = (device_index, stream_ptr(device_index) if stream is None else stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", device_index))

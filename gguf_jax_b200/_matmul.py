@@ -44,7 +44,15 @@ def _fused() -> dict[QT, FusedEntry]:
 
     def entry(qt: QT) -> FusedEntry:
         code = int(qt)
-        return kernels.fused_matmul, lambda w: int(L.ggq_fused_batch_limit(code, w.shape[0], w.shape[1]))
+        caps: dict[tuple[int, int], int] = {}       # the library's answer depends on the shape only
+
+        def cap(w) -> int:
+            got = caps.get(w.shape)
+            if got is None:
+                got = caps[w.shape] = int(L.ggq_fused_batch_limit(code, w.shape[0], w.shape[1]))
+            return got
+
+        return kernels.fused_matmul, cap
 
     return {qt: entry(qt) for qt in QT if qt in GGML_QUANT_SIZES and L.ggq_has_fused(int(qt))}
 

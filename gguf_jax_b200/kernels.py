@@ -94,7 +94,7 @@ def fused_matmul(x: torch.Tensor, w: QuantizedArray, *, out_dtype=torch.bfloat16
         if host_x and m > 0:
             # first thing, so that the fetch runs on the GPU while the host prepares the product's launch
             nbytes = m * k_dim * 2
-            xd = _backend.staging(dev, nbytes)
+            xd = _backend.staging(dev, nbytes, stream)
             _lib.check(L.ggq_stage_host(x_ptr, xd.data_ptr(), nbytes, stream))
             x_ptr = xd.data_ptr()
         data = w.data.contiguous()
@@ -120,7 +120,7 @@ def fused_matmul(x: torch.Tensor, w: QuantizedArray, *, out_dtype=torch.bfloat16
         need = _ws_need.get(key)
         if need is None:
             need = _ws_need[key] = L.ggq_workspace_bytes(*key)
-        ws = _backend.workspace(dev, need)
+        ws = _backend.workspace(dev, need, stream)
         _lib.check(fn(key[0], data.data_ptr(), n_rows, k_dim, x_ptr, m, y.data_ptr(),
                       _backend.dtype_code(out_dtype), ws.data_ptr() if ws is not None else None,
                       ws.numel() if ws is not None else 0, stream))
