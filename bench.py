@@ -54,8 +54,9 @@ UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from
 # the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 136_000_000
-NCU_TRAFFIC_SOURCE = "profiles/q4k_gemv_m1_8192x28672.md (dram__bytes_read.sum + dram__bytes_write.sum, ncu --set full, 1 GPU, full weight)"
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 134_400_000
+NCU_TRAFFIC_SOURCE = ("profiles/q4k_gemv_m1_8192x28672.md (dram__bytes_read.sum + dram__bytes_write.sum of the kernel with TMA boxes, mean of "
+                      "three launches of one ncu metrics capture, 1 GPU, full weight)")
 
 
 def algorithmic_bytes(n: int, k: int, m: int, out_itemsize: int = 2) -> int:
