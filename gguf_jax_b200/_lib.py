@@ -129,4 +129,5 @@ def ensure_tables(device_index: int) -> None:
         if blob.nbytes != L.ggq_tables_bytes():
             raise RuntimeError(f"codebook blob is {blob.nbytes} bytes, library expects {L.ggq_tables_bytes()}")
         check(L.ggq_set_tables(device_index, blob.ctypes.data, blob.nbytes))
+        check(L.ggq_init(device_index))      # the status word that bounded device-side waits raise, outside any capture
         _tables_done.add(device_index)

@@ -78,6 +78,11 @@ int* device_status_word(int device) {
   return d.status.load(std::memory_order_acquire);
 }
 
+int* device_status_word_if_any(int device) {
+  if (device < 0 || device >= kMaxDevices) return nullptr;
+  return g_dev[device].status.load(std::memory_order_acquire);
+}
+
 int device_sm_count(int device) {
   if (device < 0 || device >= kMaxDevices) return 0;
   DeviceState& d = g_dev[device];

@@ -140,7 +140,8 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
                        workspace_bytes >= gemv_wide_workspace_bytes(qtype, N, K, M, sm_count_of(dev)) &&
                        gemv_wide_applicable(qtype, N, K, M, w, x_bf16);
   if (wide_ok) {
-    err = gemv_wide(qtype, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev), st);
+    err = gemv_wide(qtype, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, workspace, workspace_bytes, sm_count_of(dev), st, 0, nullptr,
+                    device_status_word_if_any(dev));
   } else if (tile_ok) {
     // up to tile_max batch rows per launch; a larger batch reads the weight once per tile_max rows
     err = cudaSuccess;
@@ -155,7 +156,7 @@ extern "C" int32_t ggq_gemv(int32_t qtype, const void* w, int64_t N, int64_t K, 
     for (int m = 0; m < M && err == cudaSuccess; m++)
       err = tuned((const uint8_t*)w, N, K, (const uint8_t*)x_bf16 + (size_t)m * K * 2,
                   (uint8_t*)y + (size_t)m * N * y_item, y_dtype, workspace, workspace_bytes, sm_count_of(dev),
-                  nullptr, st, nullptr);   // no bounded wait on this path: no status word needed
+                  device_status_word_if_any(dev), st, nullptr);   // the bounded waits for the TMA boxes report there once the word exists (ggq_init)
   } else if (gemv_mma_applicable(ti, N, K, M) && M >= kMmaMinBatch) {
     err = gemv_mma(ti, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, tab, st);
   } else if (gemv_stream_applicable(ti, N, K, M, w, x_bf16)) {
@@ -412,7 +413,8 @@ extern "C" int32_t ggq_gemm(int32_t qtype, const void* w, int64_t N, int64_t K, 
     for (int m0 = 0; m0 < M && err == cudaSuccess; m0 += wide_slice) {
       const int mb = M - m0 < wide_slice ? M - m0 : wide_slice;
       err = gemv_wide(qtype, (const uint8_t*)w, N, K, (const uint8_t*)x_bf16 + (size_t)m0 * K * 2, mb,
-                      (uint8_t*)y + (size_t)m0 * N * y_item, y_dtype, workspace, workspace_bytes, sms, (cudaStream_t)stream);
+                      (uint8_t*)y + (size_t)m0 * N * y_item, y_dtype, workspace, workspace_bytes, sms, (cudaStream_t)stream, 0, nullptr,
+                      device_status_word(dev));
     }
   } else if (pick == kBf16w) {
     err = gemm_bf16w(qtype, (const uint8_t*)w, N, K, x_bf16, M, y, y_dtype, device_status_word(dev), workspace, workspace_bytes, sms,

@@ -50,6 +50,7 @@ inline int block_alignment(const TypeInfo* ti) {
 // Per-device immutable state owned by the library (capi.cu).
 const uint8_t* device_tables(int device);    // nullptr until ggq_set_tables(device, ...)
 int* device_status_word(int device);         // allocated on first use (or by ggq_init), nullptr if that failed
+int* device_status_word_if_any(int device);  // the same word if it exists already; never allocates (safe under stream capture)
 int device_sm_count(int device);             // multiprocessor count, cached per device; 0 if unknown
 
 // Thread-local error text (capi.cu).

@@ -69,7 +69,9 @@ int32_t ggq_set_tables(int32_t device, const void* host_blob, size_t bytes);
  * waits raise (see ggq_read_status) and caches the multiprocessor count.  The launchers that can
  * wait (ggq_gemv_sharded, ggq_gemv_sharded_tagged, ggq_gemm) do the same on their first call on
  * a device; that first call allocates device memory, so make it -- or this call -- outside any
- * stream capture.  Thread-safe, idempotent.  No reference counterpart. */
+ * stream capture.  ggq_gemv never allocates: its kernels' waits for their own TMA copies (bounded like the others;
+ * they run out only if the copy engine fails) are reported once the word exists, i.e. after this call or one of
+ * those.  Thread-safe, idempotent.  No reference counterpart. */
 int32_t ggq_init(int32_t device);
 
 /* Decode n_blocks blocks of `qtype` (device bytes, n_blocks * block_bytes) into
